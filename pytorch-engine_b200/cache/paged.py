@@ -43,12 +43,15 @@ class CacheView:
     @property
     def k_pages(self) -> torch.Tensor:
         g = self.group
-        return g.storage[self.index, 0] if g.v_storage is None else g.storage[self.index]
+        return g.storage[self.index, 0] if g.paired else g.storage[self.index]
 
     @property
     def v_pages(self) -> torch.Tensor:
+        """The values' pages; for a group whose values are read out of the key rows, the key pages themselves."""
         g = self.group
-        return g.storage[self.index, 1] if g.v_storage is None else g.v_storage[self.index]
+        if g.paired:
+            return g.storage[self.index, 1]
+        return g.storage[self.index] if g.v_storage is None else g.v_storage[self.index]
 
     @property
     def page_table(self) -> torch.Tensor:
@@ -70,7 +73,8 @@ class CacheGroup:
     num_pages: int = 0
     pool: Optional[NumberPool] = None
     storage: Optional[torch.Tensor] = None
-    v_storage: Optional[torch.Tensor] = None   # values of their own size: then ``storage`` holds the keys only
+    v_storage: Optional[torch.Tensor] = None   # values of their own size or head count: then ``storage`` holds the keys only
+    paired: bool = False                       # ``storage`` holds keys and values side by side ([entries, 2, ...])
     page_table: Optional[torch.Tensor] = None
     pages_of_slot: Dict[int, List[int]] = field(default_factory=dict)  # logical page -> physical (-1: released)
     state_tensors: Dict[str, torch.Tensor] = field(default_factory=dict)
@@ -120,14 +124,19 @@ class PagedCache:
             g.num_pages = pages_for(self.max_tokens)
             g.pool = NumberPool(g.num_pages, "page")
             # zeros, not uninitialised memory: rows that were never written must hold finite values
-            if r.value_dim == r.head_dim:
+            if r.values_in_keys:
+                # a latent cache: one row per position that the mixer reads as key and as value
+                g.storage = torch.zeros((len(g.entries), g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
+                                        dtype=self.dtype, device=self.device)
+            elif r.value_dim == r.head_dim and r.n_value_heads == r.kv_heads:
+                g.paired = True
                 g.storage = torch.zeros((len(g.entries), 2, g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
                                         dtype=self.dtype, device=self.device)
             else:
-                # values of another size than keys: two pools of pages with the same numbering
+                # values of another size or head count than keys: two pools of pages with the same numbering
                 g.storage = torch.zeros((len(g.entries), g.num_pages, r.kv_heads, PAGE_TOKENS, r.head_dim),
                                         dtype=self.dtype, device=self.device)
-                g.v_storage = torch.zeros((len(g.entries), g.num_pages, r.kv_heads, PAGE_TOKENS, r.value_dim),
+                g.v_storage = torch.zeros((len(g.entries), g.num_pages, r.n_value_heads, PAGE_TOKENS, r.value_dim),
                                           dtype=self.dtype, device=self.device)
             g.page_table = torch.full((self.max_slots, self.table_width), -1, dtype=torch.int32, device=self.device)
         elif r.kind == "state":
@@ -236,11 +245,15 @@ class PagedCache:
             raise CacheBookkeepingError("a sequence cannot shrink by commit(); use truncate()")
         self.lengths[slot] = new_length
         for g in self.groups:
-            w = g.request.window
-            if g.request.kind != "kv" or not w:
+            w, c = g.request.window, g.request.chunk
+            if g.request.kind != "kv" or not (w or c):
                 continue
-            # the next query sits at position new_length and sees keys > new_length - w
-            first_needed = max(0, new_length - w + 1) // PAGE_TOKENS
+            # the next query sits at position new_length and sees keys > new_length - w, and with a chunk mask the
+            # keys of its own block of c positions
+            first_key = max(0, new_length - w + 1) if w else 0
+            if c:
+                first_key = max(first_key, new_length // c * c)
+            first_needed = first_key // PAGE_TOKENS
             pages = g.pages_of_slot[slot]
             for logical in range(min(first_needed, len(pages))):
                 if pages[logical] >= 0:
@@ -253,7 +266,7 @@ class PagedCache:
         if length > self.lengths[slot]:
             raise CacheBookkeepingError("truncate() cannot lengthen a sequence")
         for g in self.groups:
-            if g.request.kind == "state" or g.request.window:
+            if g.request.kind == "state" or g.request.window or g.request.chunk:
                 if length != self.lengths[slot]:
                     raise CacheBookkeepingError("a sequence with windowed or fixed-size state cannot be truncated")
         keep = pages_for(length)

@@ -6,6 +6,7 @@ from .registry import (Architecture, architecture, architecture_names, architect
 from .qwen3 import Qwen3Config
 from .vabelorn import VabelornConfig
 from .lunadra import LunadraConfig
+from .vemepel import VemepelConfig
 
 __all__ = [
     "ConfigError", "ModelConfig", "read_config_dict", "Architecture", "architecture", "architecture_names",

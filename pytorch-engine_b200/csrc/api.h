@@ -24,6 +24,12 @@ int pe_attention_generic_ex(int dtype, int decode, const void* q, long long q_ld
     const int* seq_past, const int* seq_slot, const int* page_table, int table_stride, int num_pages,
     const void* k_pages, const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
     cudaStream_t stream);
+int pe_attention_generic_masked(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
+    int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int chunk,
+    int v_ld, int v_heads, int out_f32, int sink, const float* out_cos, const float* out_sin, int out_rot, int out_rows, int out_inter,
+    const int* seq_qstart, const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
+    int num_pages, const void* k_pages, const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
+    cudaStream_t stream);
 int pe_attention_decode_noalloc(int dtype, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs,
     int n_heads, int n_kv_heads, int head_dim, float scale, int window, const int* seq_qstart, const int* seq_past,
     const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
@@ -54,6 +60,26 @@ int pe_attention_umma_prefill_ex(const void* q, long long q_ld, long long n_toke
     const float* out_cos, const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past,
     const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
     const void* v_pages, int n_sms, int* work_counter, int* status, cudaStream_t stream);
+
+// stream_parts.cu
+int pe_norm_token_shift(int out_dtype, const float* x, const float* w, float eps, const float* mix, float* state,
+    const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out, int n_tokens, int width, int n_slots,
+    int* status, cudaStream_t stream);
+int pe_depth_average(const float* results, long long layer_stride, const float* coeff, int n_terms, float* out,
+    float* copy, long long n, cudaStream_t stream);
+int pe_polynorm(int dtype, const void* z, const float* coeff, float eps, void* out, int n_rows, int width,
+    cudaStream_t stream);
+int pe_sigmoid_gate(int dtype, void* x, long long x_ld, const void* g, long long g_ld, int n_tokens, int heads, int dv,
+    int per_head, cudaStream_t stream);
+int pe_diff_combine(int dtype, const float* a, void* out, int n_tokens, int heads, int dv, float lambda, float eps,
+    float post, cudaStream_t stream);
+int pe_rows_to_pages(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int n_tokens,
+    const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table, int table_stride,
+    int num_pages, void* pages, int* status, cudaStream_t stream);
+int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q_col0, int low_col0, int heads, int d, int dr,
+    int rank, const float* norm_w, float eps, const float* cos_t, const float* sin_t, int rot, int table_rows,
+    int n_tokens, const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table,
+    int table_stride, int num_pages, void* pages, void* qfull, int write_cache, int* status, cudaStream_t stream);
 
 // embedding.cu
 int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,
@@ -157,6 +183,8 @@ long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int
 
 // moe.cu
 int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,
+    float* weight, int* dense_rows, int n_real, cudaStream_t stream);
+int pe_moe_route_logits(const float* logits, const float* bias, int n_tokens, int n_all, int top, int* chosen,
     float* weight, int* dense_rows, int n_real, cudaStream_t stream);
 int pe_moe_group(const int* chosen, int n_tokens, int top, int n_real, int* offsets, int* row_token, int* pair_row,
     cudaStream_t stream);

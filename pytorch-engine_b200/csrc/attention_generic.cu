@@ -44,7 +44,23 @@ struct AttnArgs {
   const float* out_cos;               // [out_rows, out_rot/2]: the head's output at position p is turned by -angle(p)
   const float* out_sin;               //   (values were cached turned by their own positions); null: not turned
   int out_rot, out_rows, out_inter;   // features turned, rows of the tables, layout of pairs (1: 2m with 2m+1)
+  // other masks and layouts (defaults: chunk = 0, v_ld = v_dim, v_heads = n_kv_heads)
+  int chunk;                          // > 0: a key is visible only inside the query's own block of `chunk` positions,
+                                      //   blocks counted from position 0 of the sequence
+  int v_ld;                           // floats or halves between two value rows of a page (values that are the leading
+                                      //   features of wider rows: the key rows themselves for a latent cache)
+  int v_heads;                        // value heads in a page; kv head g reads value head g % v_heads (several key
+                                      //   maps over one set of values)
+  int out_f32;                        // != 0: `out` is float32 whatever the inputs' type (not with a turned output)
 };
+
+// First visible key of a query at `qpos` under the window and chunk masks.
+__device__ __forceinline__ int first_visible(const AttnArgs& a, int qpos) {
+  int lo = 0;
+  if (a.window > 0) lo = max(lo, qpos - a.window + 1);
+  if (a.chunk > 0) lo = max(lo, qpos / a.chunk * a.chunk);
+  return lo;
+}
 
 // Turn a head's output row (float32, in shared or local memory `src`) back by the angle of position `pos` and store it.
 template <typename T>
@@ -75,16 +91,17 @@ __device__ __forceinline__ void load_tile(const AttnArgs& a, int slot, int kvh, 
   if (!ok && tid == 0 && k0 < k_end) report(a.status, kStatusPageOutOfRange, slot, page, k0);
   const size_t base = ((size_t)(ok ? page : 0) * a.n_kv_heads + kvh) * kPageTokens + (k0 % kPageTokens);
   const T* kp = (const T*)a.k_pages + base * d;
-  const T* vp = (const T*)a.v_pages + base * dv;
+  const size_t vbase = ((size_t)(ok ? page : 0) * a.v_heads + (kvh % a.v_heads)) * kPageTokens + (k0 % kPageTokens);
+  const T* vp = (const T*)a.v_pages + vbase * a.v_ld;
   for (int i = tid; i < kTileKeys * d; i += nthreads) {
     const int r = i / d, c = i - r * d;
     const bool live = ok && (k0 + r) < k_end;
     Ks[r * (d + 1) + c] = live ? to_f32<T>(kp[i]) : 0.f;
   }
   for (int i = tid; i < kTileKeys * dv; i += nthreads) {
-    const int r = i / dv;
+    const int r = i / dv, c = i - r * dv;
     const bool live = ok && (k0 + r) < k_end;
-    Vs[i] = live ? to_f32<T>(vp[i]) : 0.f;
+    Vs[i] = live ? to_f32<T>(vp[(size_t)r * a.v_ld + c]) : 0.f;
   }
 }
 
@@ -178,18 +195,17 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
   }
-  int k_begin = 0;
-  if (a.window > 0) k_begin = max(0, (past + first) - a.window + 1) / kTileKeys * kTileKeys;
+  const int k_begin = first_visible(a, past + first) / kTileKeys * kTileKeys;   // of the block's first query
   const int k_end = last_pos + 1;
+  const int my_lo = first_visible(a, qpos);
   for (int k0 = k_begin; k0 < k_end; k0 += kTileKeys) {
     __syncthreads();  // everyone is done with the previous tile (and q is written, first time)
     load_tile<T>(a, slot, kvh, k0, k_end, Ks, Vs, threadIdx.x, blockDim.x);
     __syncthreads();
     if (!active || k0 > qpos) continue;  // the whole tile lies in this query's future
     const int kpos = k0 + lane;
-    bool visible = kpos <= qpos;
-    if (a.window > 0) visible = visible && (kpos > qpos - a.window);
-    if (a.window > 0 && k0 + kTileKeys - 1 <= qpos - a.window) continue;  // whole tile before the window
+    const bool visible = kpos <= qpos && kpos >= my_lo;
+    if (k0 + kTileKeys - 1 < my_lo) continue;  // the whole tile lies before what this query sees
     fold_tile<DPL>(qs, Ks, Vs, d, dv, n_here, a.scale, visible, lane, m, l, acc);
   }
   if (!active) return;
@@ -215,10 +231,14 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
       store_unrotated<T>(a, qs, o, qpos, lane, 32);
       continue;
     }
+    float* of = (float*)a.out + (size_t)(q0 + my_row) * a.out_ld + (size_t)(h0 + h) * dv;
 #pragma unroll
     for (int i = 0; i < DPL; ++i) {
       const int c = lane + 32 * i;
-      if (c < dv) o[c] = from_f32<T>(acc[h][i] * inv);
+      if (c < dv) {
+        if (a.out_f32) of[c] = acc[h][i] * inv;
+        else o[c] = from_f32<T>(acc[h][i] * inv);
+      }
     }
   }
 }
@@ -249,8 +269,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
   const int len = qpos + 1;
   int k_lo = split * a.split_keys, k_hi = min(len, k_lo + a.split_keys);
   if (k_lo >= len) return;
-  const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
-  if (k_hi <= win_lo) return;                    // the whole range lies before the window
+  const int win_lo = first_visible(a, qpos);
+  if (k_hi <= win_lo) return;                    // the whole range lies before the window or the chunk
   const int slot = a.seq_slot[b];
   for (int i = threadIdx.x; i < kGT * d; i += blockDim.x) {
     const int h = i / d, c = i - h * d;
@@ -328,7 +348,7 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
     if (threadIdx.x == 0) report(a.status, kStatusPositionOutOfRange, b, len - 1, a.split_keys * a.max_splits);
     n_splits = a.max_splits;
   }
-  const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
+  const int win_lo = first_visible(a, len - 1);
   const int first = min(win_lo / a.split_keys, n_splits);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   float mx = a.sink ? 0.f : -INFINITY;   // the sink is one more range whose log-sum is 0 and whose output is 0
@@ -348,6 +368,7 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
       v = fmaf(w, a.part_acc[(base + s) * d + c], v);
     }
     if (a.out_cos) orow[c] = v;
+    else if (a.out_f32) ((float*)a.out)[(size_t)t * a.out_ld + (size_t)h * d + c] = v;
     else o[c] = from_f32<T>(v);
   }
   if (a.out_cos) {
@@ -407,7 +428,7 @@ static int launch_decode(const AttnArgs& a, int n_seqs, cudaStream_t stream) {
 
 template <typename T>
 static int dispatch(const AttnArgs& a, int n_seqs, int max_q, bool decode, cudaStream_t stream) {
-  if (a.head_dim > 512 || a.v_dim > 512) return PE_ERR_UNSUPPORTED_SIZE;
+  if (a.head_dim > 1024 || a.v_dim > 512) return PE_ERR_UNSUPPORTED_SIZE;   // and what fits shared memory (launch_*)
   const int d = a.v_dim;   // output features per lane
   if (decode) {
     if (d <= 32) return launch_decode<T, 1, 4>(a, n_seqs, stream);
@@ -452,10 +473,29 @@ extern "C" int pe_attention_generic_ex(int dtype, int decode, const void* q, lon
                                        const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
                                        int num_pages, const void* k_pages, const void* v_pages, float* scratch,
                                        int split_keys, int max_splits, int* status, cudaStream_t stream) {
+  return pe_attention_generic_masked(dtype, decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim,
+                                     v_dim, scale, window, 0, v_dim, n_kv_heads, 0, sink, out_cos, out_sin, out_rot, out_rows,
+                                     out_inter, seq_qstart, seq_past, seq_slot, page_table, table_stride, num_pages,
+                                     k_pages, v_pages, scratch, split_keys, max_splits, status, stream);
+}
+
+// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), value rows
+// `v_ld` elements apart (>= v_dim), `v_heads` value heads a page (kv head g reads value head g % v_heads), and
+// optionally a float32 output (`out_f32`: out_ld then counts floats).
+extern "C" int pe_attention_generic_masked(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
+                                           int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim,
+                                           float scale, int window, int chunk, int v_ld, int v_heads, int out_f32, int sink,
+                                           const float* out_cos, const float* out_sin, int out_rot, int out_rows,
+                                           int out_inter, const int* seq_qstart, const int* seq_past, const int* seq_slot,
+                                           const int* page_table, int table_stride, int num_pages, const void* k_pages,
+                                           const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
+                                           cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || v_dim <= 0 || n_heads % n_kv_heads) return PE_ERR_BAD_ARGUMENT;
   if (out_cos && (!out_sin || out_rot <= 0 || out_rot > v_dim || (out_rot & 1))) return PE_ERR_BAD_ARGUMENT;
+  if (v_ld < v_dim || v_heads <= 0 || chunk < 0 || (out_f32 && out_cos)) return PE_ERR_BAD_ARGUMENT;
   pe::AttnArgs a;
+  a.chunk = chunk; a.v_ld = v_ld; a.v_heads = v_heads; a.out_f32 = out_f32;
   a.v_dim = v_dim; a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin;
   a.out_rot = out_cos ? out_rot : 0; a.out_rows = out_rows; a.out_inter = out_inter;
   a.q = q; a.q_ld = q_ld; a.out = out; a.out_ld = out_ld;
@@ -531,6 +571,7 @@ extern "C" int pe_attention_decode_noalloc(int dtype, const void* q, long long q
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = k_pages; a.v_pages = v_pages; a.status = status;
   a.split_keys = split_keys; a.max_splits = max_splits;
+  a.chunk = 0; a.v_ld = head_dim; a.v_heads = n_kv_heads; a.out_f32 = 0;
   a.v_dim = head_dim; a.sink = 0; a.out_cos = nullptr; a.out_sin = nullptr; a.out_rot = 0; a.out_rows = 0; a.out_inter = 0;
   a.part_acc = scratch;
   a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;

@@ -3,6 +3,7 @@
 //
 //   route     s = softmax(z) over all router outputs; the `top` largest of s + correction are chosen (ties: the
 //             lower index), each weighted with its own s (not renormalised); all in float32
+//   route by logits   the `top` largest of z + bias are chosen, weighted by a softmax over the chosen ones alone
 //   group     pairs whose choice is a real expert (index < n_real) are ordered by expert: offsets[e] .. offsets[e+1]
 //             are expert e's rows, row_token[r] the token of row r, pair_row[t, j] the row of a pair (-1: the
 //             choice is an identity expert, which returns its input)
@@ -56,6 +57,49 @@ __global__ void moe_route_kernel(const float* logits, const float* __restrict__ 
       // where every expert runs on every token, the pair's row is known here
       if (dense_rows) dense_rows[(size_t)t * top + j] = (any && best_e < n_real) ? t * n_real + best_e : -1;
     }
+  }
+}
+
+// The choice by the logits themselves: z' = z + bias, the `top` largest z' (ties: the lower index), weighted by a
+// softmax over the chosen z' alone.  One warp per token.
+__global__ void moe_route_logits_kernel(const float* logits, const float* __restrict__ bias, int n_tokens, int n_all, int top,
+                                        int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ dense_rows,
+                                        int n_real) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const int t = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * n_all;
+  unsigned long long taken_lo = 0ull;   // this lane's entries e = lane + 32 * i, bit i set once chosen (n_all <= 2048)
+  float first = 0.f, sum = 0.f;
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane, i = 0; e < n_all; e += 32, ++i) {
+      if ((taken_lo >> i) & 1ull) continue;
+      const float c = z[e] + (bias ? bias[e] : 0.f);
+      if (c > best || best_e == 0x7fffffff) { best = c; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
+    }
+    if (best_e != 0x7fffffff && (best_e & 31) == lane) taken_lo |= 1ull << (best_e >> 5);
+    if (j == 0) first = best;            // the largest chosen logit: the softmax's reference
+    const float w = expf(best - first);
+    sum += w;
+    if (lane == 0) {
+      chosen[(size_t)t * top + j] = best_e;
+      weight[(size_t)t * top + j] = w;
+      if (dense_rows) dense_rows[(size_t)t * top + j] = best_e < n_real ? t * n_real + best_e : -1;
+    }
+  }
+  if (lane == 0) {
+    const float inv = 1.f / sum;
+    for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] *= inv;
   }
 }
 
@@ -333,6 +377,18 @@ extern "C" int pe_moe_route(const float* logits, const float* correction, int n_
   if (n_all > 2048) return PE_ERR_UNSUPPORTED_SIZE;
   const int warps = 4;
   pe::launch(pe::moe_route_kernel, (n_tokens + warps - 1) / warps, warps * 32, 0, stream, logits, correction, n_tokens, n_all,
+             top, chosen, weight, dense_rows, n_real);
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_moe_route_logits(const float* logits, const float* bias, int n_tokens, int n_all, int top, int* chosen,
+                                   float* weight, int* dense_rows, int n_real, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (n_all <= 0 || top <= 0 || top > n_all) return PE_ERR_BAD_ARGUMENT;
+  if (n_all > 2048) return PE_ERR_UNSUPPORTED_SIZE;
+  const int warps = 4;
+  pe::launch(pe::moe_route_logits_kernel, (n_tokens + warps - 1) / warps, warps * 32, 0, stream, logits, bias, n_tokens, n_all,
              top, chosen, weight, dense_rows, n_real);
   PE_LAUNCH_CHECK();
   return PE_OK;

@@ -1,0 +1,325 @@
+// Small parts around the residual stream and the mixers' inputs and outputs, all in float32 arithmetic:
+//
+//   norm_token_shift   h[t] = x[t] / rms(x[t]) * w ;  out[t] = h[t] + (h[t-1] - h[t]) * mix, where a sequence's first token
+//                      of the step takes the row that the sequence kept (zeros at its start), and the sequence's last
+//                      h of the step is kept for the next one
+//   depth_average      out = sum_j coeff[j] * results[j]  over the results of the embedding and of every block so far
+//   polynorm           a N(z) + b N(z^2) + c N(z^3) + e,  N(u) = u / sqrt(mean(u^2) + eps) over a token's row
+//   sigmoid_gate       x[t, h, :] *= sigmoid(g[t, h])  (one gate a head)  or  x[t, c] *= sigmoid(g[t, c])
+//   diff_combine       o = a1 - lambda * a2 ;  out = o / sqrt(mean(o^2) + eps) * post  per (token, head)
+//   rows_to_pages      rows of a step's tokens copied into the pages of their sequences (keys, values or latent rows)
+//   latent_prepare     a latent-attention layer's cached row and the rotated part of its queries (see the kernel)
+#include "api.h"
+#include "common.cuh"
+
+namespace pe {
+
+// grid: tokens; block: threads over the width.
+template <typename T>
+__global__ void __launch_bounds__(256) norm_token_shift_kernel(const float* x, const float* __restrict__ w, float eps,
+                                                               const float* __restrict__ mix, float* state,
+                                                               const int* token_seq, const int* seq_slot,
+                                                               const int* seq_qstart, T* __restrict__ out, int n_tokens,
+                                                               int width, int n_slots, int* status) {
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const bool first = t == seq_qstart[b];
+  const int slot = seq_slot[b];
+  if (first && (slot < 0 || slot >= n_slots)) {
+    if (threadIdx.x == 0) report(status, kStatusSlotOutOfRange, t, slot, n_slots);
+    return;
+  }
+  const float* cur = x + (size_t)t * width;
+  // the other row this block needs: the previous token's, or (first token) the sequence's last row of the step
+  const float* other = first ? x + (size_t)(seq_qstart[b + 1] - 1) * width : cur - width;
+  float s0 = 0.f, s1 = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float a = cur[c], o = other[c];
+    s0 = fmaf(a, a, s0);
+    s1 = fmaf(o, o, s1);
+  }
+  s0 = block_sum(s0, red);
+  s1 = block_sum(s1, red);
+  const float inv0 = rsqrtf(s0 / (float)width + eps), inv1 = rsqrtf(s1 / (float)width + eps);
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float h = cur[c] * inv0 * w[c];
+    const float ho = other[c] * inv1 * w[c];
+    float hp = ho;
+    if (first) {
+      // this thread alone reads and writes the element: the kept row is read before it is replaced
+      hp = state[(size_t)slot * width + c];
+      state[(size_t)slot * width + c] = ho;
+    }
+    out[(size_t)t * width + c] = from_f32<T>(fmaf(hp - h, mix[c], h));
+  }
+}
+
+__global__ void depth_average_kernel(const float* results, long long layer_stride, const float* __restrict__ coeff,
+                                     int n_terms, float* __restrict__ out, float* __restrict__ copy, long long n) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+    float acc = 0.f;
+    for (int j = 0; j < n_terms; ++j) acc = fmaf(coeff[j], results[(size_t)j * layer_stride + i], acc);
+    out[i] = acc;
+    if (copy) copy[i] = acc;
+  }
+}
+
+// grid: rows; the row is read twice (sums, then values).
+template <typename T>
+__global__ void __launch_bounds__(256) polynorm_kernel(const T* z, const float* __restrict__ coeff, float eps,
+                                                       T* __restrict__ out, int width) {
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const T* row = z + (size_t)blockIdx.x * width;
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(row[c]), v2 = v * v, v3 = v2 * v;
+    s1 = fmaf(v, v, s1);
+    s2 = fmaf(v2, v2, s2);
+    s3 = fmaf(v3, v3, s3);
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  s3 = block_sum(s3, red);
+  const float n = (float)width;
+  const float f1 = coeff[0] * rsqrtf(s1 / n + eps), f2 = coeff[1] * rsqrtf(s2 / n + eps), f3 = coeff[2] * rsqrtf(s3 / n + eps);
+  const float e = coeff[3];
+  for (int c = threadIdx.x; c < width; c += blockDim.x) {
+    const float v = to_f32<T>(row[c]), v2 = v * v;
+    out[(size_t)blockIdx.x * width + c] = from_f32<T>(fmaf(f1, v, fmaf(f2, v2, fmaf(f3, v2 * v, e))));
+  }
+}
+
+template <typename T>
+__global__ void sigmoid_gate_kernel(T* x, long long x_ld, const T* g, long long g_ld, int n_tokens, int heads, int dv,
+                                    int per_head) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int row = heads * dv;
+  const size_t total = (size_t)n_tokens * row;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const int t = (int)(i / row), c = (int)(i - (size_t)t * row);
+    const float z = to_f32<T>(g[(size_t)t * g_ld + (per_head ? c / dv : c)]);
+    T* p = x + (size_t)t * x_ld + c;
+    *p = from_f32<T>(to_f32<T>(*p) / (1.f + expf(-z)));
+  }
+}
+
+// One warp per (token, head).  a: float32 [n, 2 * heads, dv] with the first map's heads first.
+template <typename T>
+__global__ void diff_combine_kernel(const float* a, T* __restrict__ out, int n_tokens, int heads, int dv, float lambda,
+                                    float eps, float post) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31;
+  const long long item = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long long)n_tokens * heads) return;
+  const int t = (int)(item / heads), h = (int)(item - (long long)t * heads);
+  const float* a1 = a + ((size_t)t * 2 * heads + h) * dv;
+  const float* a2 = a1 + (size_t)heads * dv;
+  float ss = 0.f;
+  for (int c = lane; c < dv; c += 32) {
+    const float o = fmaf(-lambda, a2[c], a1[c]);
+    ss = fmaf(o, o, ss);
+  }
+  ss = warp_sum(ss);
+  const float f = rsqrtf(ss / (float)dv + eps) * post;
+  T* o_row = out + ((size_t)t * heads + h) * dv;
+  for (int c = lane; c < dv; c += 32)
+    o_row[c] = from_f32<T>(fmaf(-lambda, a2[c], a1[c]) * f);
+}
+
+// Where a token's row lies in the pages of its sequence; -1 (and a status report) if the page table has none.
+__device__ __forceinline__ long long page_row(int t, const int* token_seq, const int* token_pos, const int* seq_slot,
+                                              const int* page_table, int table_stride, int num_pages, int* status) {
+  const int pos = token_pos[t];
+  const int slot = seq_slot[token_seq[t]];
+  const int logical = pos / kPageTokens;
+  int page = -1;
+  if (pos >= 0 && logical < table_stride) page = page_table[(size_t)slot * table_stride + logical];
+  if (page < 0 || page >= num_pages) {
+    if (threadIdx.x == 0) report(status, kStatusPageOutOfRange, slot, page, pos);
+    return -1;
+  }
+  return (long long)page * kPageTokens + (pos % kPageTokens);
+}
+
+// pages: [num_pages, heads, 64, dim]; src row t holds heads * dim features from column col0.  grid: tokens.
+template <typename T>
+__global__ void rows_to_pages_kernel(const T* src, long long src_ld, int col0, int heads, int dim, const int* token_seq,
+                                     const int* token_pos, const int* seq_slot, const int* page_table, int table_stride,
+                                     int num_pages, T* __restrict__ pages, int* status) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const long long pr = page_row(t, token_seq, token_pos, seq_slot, page_table, table_stride, num_pages, status);
+  if (pr < 0) return;
+  const long long page = pr / kPageTokens, r = pr % kPageTokens;
+  const T* row = src + (size_t)t * src_ld + col0;
+  for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
+    const int h = i / dim, c = i - h * dim;
+    pages[(((size_t)page * heads + h) * kPageTokens + r) * dim + c] = row[i];
+  }
+}
+
+// A latent-attention layer's step, per token (grid: tokens).  x row: [.. q: heads x (d + dr) at q_col0 ..
+// low: rank + dr at low_col0 ..].
+//   cached row  = [ low[:rank] / rms(low[:rank]) * norm_w | turn(low[rank:]) ]        -> pages [num_pages, 1, 64, rank + dr]
+//   qfull[t, h] = [ (left as it is: the absorbed query is written by a product) | turn(q[h, d:]) ]   [n, heads, rank + dr]
+// turn: adjacent pairs (2i, 2i+1) of the first `rot` features by the angle tables' row of the token's position.
+template <typename T>
+__global__ void __launch_bounds__(256) latent_prepare_kernel(const T* x, long long x_ld, int q_col0, int low_col0, int heads,
+                                                             int d, int dr, int rank, const float* __restrict__ norm_w,
+                                                             float eps, const float* __restrict__ cos_t,
+                                                             const float* __restrict__ sin_t, int rot, int table_rows,
+                                                             const int* token_seq, const int* token_pos, const int* seq_slot,
+                                                             const int* page_table, int table_stride, int num_pages,
+                                                             T* __restrict__ pages, T* __restrict__ qfull, int write_cache,
+                                                             int* status) {
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int pos = token_pos[t];
+  const T* row = x + (size_t)t * x_ld;
+  const int half = rot / 2;
+  if (rot > 0 && (pos < 0 || pos >= table_rows)) {
+    if (threadIdx.x == 0) report(status, kStatusPositionOutOfRange, t, pos, table_rows);
+    return;
+  }
+  const float* cs = cos_t + (size_t)pos * half;
+  const float* sn = sin_t + (size_t)pos * half;
+  // the rotated part of every head's query
+  const int wide = rank + dr;
+  for (int i = threadIdx.x; i < heads * dr; i += blockDim.x) {
+    const int h = i / dr, c = i - h * dr;
+    const T* q = row + q_col0 + (size_t)h * (d + dr) + d;
+    float v = to_f32<T>(q[c]);
+    if (c < rot) {
+      const int m = c >> 1;
+      const float o = to_f32<T>(q[c ^ 1]);
+      v = (c & 1) ? fmaf(v, cs[m], o * sn[m]) : fmaf(v, cs[m], -o * sn[m]);
+    }
+    qfull[((size_t)t * heads + h) * wide + rank + c] = from_f32<T>(v);
+  }
+  if (!write_cache) return;
+  const T* low = row + low_col0;
+  float ss = 0.f;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) {
+    const float v = to_f32<T>(low[c]);
+    ss = fmaf(v, v, ss);
+  }
+  ss = block_sum(ss, red);
+  const float inv = rsqrtf(ss / (float)rank + eps);
+  const long long pr = page_row(t, token_seq, token_pos, seq_slot, page_table, table_stride, num_pages, status);
+  if (pr < 0) return;
+  T* dst = pages + (size_t)pr * wide;
+  for (int c = threadIdx.x; c < rank; c += blockDim.x) dst[c] = from_f32<T>(to_f32<T>(low[c]) * inv * norm_w[c]);
+  for (int c = threadIdx.x; c < dr; c += blockDim.x) {
+    float v = to_f32<T>(low[rank + c]);
+    if (c < rot) {
+      const int m = c >> 1;
+      const float o = to_f32<T>(low[rank + (c ^ 1)]);
+      v = (c & 1) ? fmaf(v, cs[m], o * sn[m]) : fmaf(v, cs[m], -o * sn[m]);
+    }
+    dst[rank + c] = from_f32<T>(v);
+  }
+}
+
+static int flat_blocks(size_t total, int threads) {
+  size_t blocks = (total + threads - 1) / threads;
+  if (blocks > (size_t)kSMs * 16) blocks = (size_t)kSMs * 16;
+  return (int)(blocks ? blocks : 1);
+}
+
+}  // namespace pe
+
+#define PE_BY_DTYPE(dtype, CALL)                       \
+  if ((dtype) == PE_F32) { using T = float; CALL; }    \
+  else if ((dtype) == PE_BF16) { using T = __nv_bfloat16; CALL; } \
+  else return PE_ERR_UNSUPPORTED_DTYPE;
+
+extern "C" int pe_norm_token_shift(int out_dtype, const float* x, const float* w, float eps, const float* mix, float* state,
+                                   const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out, int n_tokens,
+                                   int width, int n_slots, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (width <= 0 || n_slots <= 0) return PE_ERR_BAD_ARGUMENT;
+  PE_BY_DTYPE(out_dtype, pe::launch(pe::norm_token_shift_kernel<T>, n_tokens, 256, 0, stream, x, w, eps, mix, state, token_seq,
+                                    seq_slot, seq_qstart, (T*)out, n_tokens, width, n_slots, status));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_depth_average(const float* results, long long layer_stride, const float* coeff, int n_terms, float* out,
+                                float* copy, long long n, cudaStream_t stream) {
+  if (n <= 0) return PE_OK;
+  if (n_terms <= 0 || layer_stride < n) return PE_ERR_BAD_ARGUMENT;
+  pe::launch(pe::depth_average_kernel, pe::flat_blocks((size_t)n, 256), 256, 0, stream, results, layer_stride, coeff, n_terms,
+             out, copy, n);
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_polynorm(int dtype, const void* z, const float* coeff, float eps, void* out, int n_rows, int width,
+                           cudaStream_t stream) {
+  if (n_rows <= 0) return PE_OK;
+  if (width <= 0) return PE_ERR_BAD_ARGUMENT;
+  PE_BY_DTYPE(dtype, pe::launch(pe::polynorm_kernel<T>, n_rows, 256, 0, stream, (const T*)z, coeff, eps, (T*)out, width));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_sigmoid_gate(int dtype, void* x, long long x_ld, const void* g, long long g_ld, int n_tokens, int heads,
+                               int dv, int per_head, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (heads <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
+  const int blocks = pe::flat_blocks((size_t)n_tokens * heads * dv, 256);
+  PE_BY_DTYPE(dtype, pe::launch(pe::sigmoid_gate_kernel<T>, blocks, 256, 0, stream, (T*)x, x_ld, (const T*)g, g_ld, n_tokens,
+                                heads, dv, per_head));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_diff_combine(int dtype, const float* a, void* out, int n_tokens, int heads, int dv, float lambda, float eps,
+                               float post, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (heads <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
+  const long long items = (long long)n_tokens * heads;
+  const int blocks = (int)((items + 7) / 8);
+  PE_BY_DTYPE(dtype, pe::launch(pe::diff_combine_kernel<T>, blocks, 256, 0, stream, a, (T*)out, n_tokens, heads, dv,
+                                lambda, eps, post));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_rows_to_pages(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int n_tokens,
+                                const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table,
+                                int table_stride, int num_pages, void* pages, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (heads <= 0 || dim <= 0 || col0 < 0) return PE_ERR_BAD_ARGUMENT;
+  PE_BY_DTYPE(dtype, pe::launch(pe::rows_to_pages_kernel<T>, n_tokens, 128, 0, stream, (const T*)src, src_ld, col0, heads, dim,
+                                token_seq, token_pos, seq_slot, page_table, table_stride, num_pages, (T*)pages, status));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q_col0, int low_col0, int heads, int d, int dr,
+                                 int rank, const float* norm_w, float eps, const float* cos_t, const float* sin_t, int rot,
+                                 int table_rows, int n_tokens, const int* token_seq, const int* token_pos,
+                                 const int* seq_slot, const int* page_table, int table_stride, int num_pages, void* pages,
+                                 void* qfull, int write_cache, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (heads <= 0 || d <= 0 || dr < 0 || rank <= 0 || rot < 0 || rot > dr || (rot & 1)) return PE_ERR_BAD_ARGUMENT;
+  if (rot > 0 && (!cos_t || !sin_t)) return PE_ERR_BAD_ARGUMENT;
+  PE_BY_DTYPE(dtype, pe::launch(pe::latent_prepare_kernel<T>, n_tokens, 256, 0, stream, (const T*)x, x_ld, q_col0, low_col0,
+                                heads, d, dr, rank, norm_w, eps, cos_t, sin_t, rot, table_rows, token_seq, token_pos, seq_slot,
+                                page_table, table_stride, num_pages, (T*)pages, (T*)qfull, write_cache, status));
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}

@@ -56,9 +56,9 @@ class DecoderModel:
 
     @staticmethod
     def cache_key(entry: int, block_spec, mixer_name: str):
-        """The cache's key for one mixer of a run: the entry number itself for a block with one mixer,
-        ``(entry, mixer name)`` for a block with several."""
-        return entry if len(block_spec.mixer_names()) <= 1 else (entry, mixer_name)
+        """The cache's key for one part of a run that keeps something: the entry number itself for a block with one
+        such part (its mixer), ``(entry, part name)`` for a block with several."""
+        return entry if len(block_spec.keeper_names()) <= 1 else (entry, mixer_name)
 
     # the cache key of what the embedding keeps per sequence (an embedding of token pairs keeps the last token)
     EMBEDDING_KEY = (-1, "embedding")
@@ -71,30 +71,32 @@ class DecoderModel:
             reqs[self.EMBEDDING_KEY] = emb.cache_request(self.plan.embedding.params)
         written = set()
         for run in self.plan.order:
-            if not run.writes_cache or run.cache_entry in written:
-                continue
-            written.add(run.cache_entry)
             b = self.plan.blocks[run.block]
-            for name in b.mixer_names():
-                spec = b.part(name)
-                cls = lookup("mixer", spec.kind)
-                reqs[self.cache_key(run.cache_entry, b, name)] = (
+            for name in b.keeper_names():
+                entry = run.entry_of(name)
+                if not run.writes(name) or (entry, name) in written:
+                    continue
+                written.add((entry, name))
+                role, spec = b.parts[name]
+                cls = lookup(role, spec.kind)
+                reqs[self.cache_key(entry, b, name)] = (
                     cls.cache_request(spec.params) if hasattr(cls, "cache_request") else None)
         for run in self.plan.order:
-            if run.cache_entry not in written:
-                raise ValueError(f"block {run.block} reads cache entry {run.cache_entry}, which no block writes")
+            for name in self.plan.blocks[run.block].keeper_names():
+                if (run.entry_of(name), name) not in written:
+                    raise ValueError(f"block {run.block} reads cache entry {run.entry_of(name)}, which no block writes")
         return reqs
 
     def _view(self, cache, run):
         """What a block's arrangement gets as its cache view: the view of its one mixer, a dict of
         views by mixer name for a block with several, None for a block without a mixer."""
         b = self.plan.blocks[run.block]
-        names = b.mixer_names()
+        names = b.keeper_names()
         if not names:
             return None
         if len(names) == 1:
             return cache.view(run.cache_entry)
-        return {name: cache.view((run.cache_entry, name)) for name in names}
+        return {name: cache.view((run.entry_of(name), name)) for name in names}
 
     def forward(self, ctx, cache) -> torch.Tensor:
         """Run the step described by ``ctx``; returns float32 logits ``[n_want, vocab]``."""

@@ -90,12 +90,12 @@ def state_bytes_per_slot(cfg) -> int:
     plan = architecture(cfg.architecture).plan(cfg)
     total = 0
     for run in plan.order:
-        if not run.writes_cache:
-            continue
         block = plan.blocks[run.block]
-        for name in block.mixer_names():
-            spec = block.part(name)
-            cls = lookup("mixer", spec.kind)
+        for name in block.keeper_names():
+            if not run.writes(name):
+                continue
+            role, spec = block.parts[name]
+            cls = lookup(role, spec.kind)
             req = cls.cache_request(spec.params) if hasattr(cls, "cache_request") else None
             if req is not None and req.kind == "state":
                 for _, shape, dtype_name in req.state_shapes:

@@ -718,3 +718,127 @@ def glu_act(gate_up: torch.Tensor, out: torch.Tensor, kind: str, limit: float = 
     check(library().pe_glu_act(dtype_tag(gate_up.dtype), _ptr(gate_up), _ptr(out), out.shape[0], out.shape[1], GLU_KINDS[kind],
                                float(limit), float(alpha), _stream()), "glu_act")
     _count(1)
+
+
+# ---- parts around the stream, and the other attentions (csrc/stream_parts.cu) ---------------------------------------------
+def moe_route_logits(logits: torch.Tensor, bias: Optional[torch.Tensor], top: int, chosen: torch.Tensor, weight: torch.Tensor,
+                     dense_rows: Optional[torch.Tensor] = None, n_real: int = 0) -> None:
+    """The ``top`` largest of ``logits + bias`` per row, weighted by a softmax over the chosen ones alone (csrc/moe.cu)."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route_logits: float32 logits")
+    n, n_all = logits.shape
+    _need(bias is None or (bias.dtype == torch.float32 and bias.numel() == n_all), "moe_route_logits: float32 bias, one per output")
+    _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top == weight.numel(),
+          "moe_route_logits: outputs")
+    _need(dense_rows is None or (dense_rows.dtype == torch.int32 and dense_rows.numel() == n * top), "moe_route_logits: dense_rows")
+    check(library().pe_moe_route_logits(_ptr(logits), _ptr(bias), n, n_all, int(top), _ptr(chosen), _ptr(weight),
+                                        _ptr(dense_rows), int(n_real), _stream()), "moe_route_logits")
+    _count(1)
+
+
+def attention_generic_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int,
+                             n_kv_heads: int, head_dim: int, v_dim: int, scale: float, seq_qstart: torch.Tensor,
+                             seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
+                             k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
+                             max_splits: int, status: torch.Tensor, *, window: int = 0, chunk: int = 0,
+                             v_ld: Optional[int] = None, v_heads: Optional[int] = None) -> None:
+    """``attention_generic_ex`` with a chunk mask (``chunk`` > 0: a query sees the keys of its own block of that many
+    positions, blocks counted from the sequence's start), value rows ``v_ld`` elements apart (values that are the leading
+    ``v_dim`` features of wider rows) and ``v_heads`` value heads a page (kv head g reads value head ``g % v_heads``)."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == k_pages.dtype == v_pages.dtype and out.dtype in (q.dtype, torch.float32),
+          "attention: q and the cache must share a dtype; out has it too, or is float32")
+    v_ld = v_dim if v_ld is None else int(v_ld)
+    v_heads = n_kv_heads if v_heads is None else int(v_heads)
+    check(library().pe_attention_generic_masked(
+        dtype_tag(q.dtype), 1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads,
+        n_kv_heads, head_dim, v_dim, float(scale), int(window), int(chunk), v_ld, v_heads,
+        1 if (out.dtype == torch.float32 and q.dtype != torch.float32) else 0, 0, None, None, 0, 0, 0,
+        _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages),
+        _ptr(v_pages), _ptr(scratch), split_keys, max_splits, _ptr(status), _stream()), "attention_generic_masked")
+    _count(2 if decode else 1)
+
+
+def norm_token_shift(x: torch.Tensor, weight: torch.Tensor, eps: float, mix: torch.Tensor, state: torch.Tensor,
+                     token_seq: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, out: torch.Tensor,
+                     status: torch.Tensor) -> None:
+    """``h = rmsnorm(x) * weight`` in float32, ``out[t] = h[t] + (h[t-1] - h[t]) * mix``; a sequence's first token of the
+    step takes ``state[slot]`` for ``h[t-1]``, and ``state[slot]`` then keeps the sequence's last ``h`` of the step."""
+    n, width = x.shape
+    _need(x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and tuple(out.shape) == (n, width)
+          and weight.dtype == mix.dtype == state.dtype == torch.float32 and weight.numel() == width == mix.numel()
+          and state.is_contiguous() and state.shape[1] == width, "norm_token_shift: shapes and dtypes")
+    check(library().pe_norm_token_shift(dtype_tag(out.dtype), _ptr(x), _ptr(weight), float(eps), _ptr(mix), _ptr(state),
+                                        _ptr(token_seq), _ptr(seq_slot), _ptr(seq_qstart), _ptr(out), n, width, state.shape[0],
+                                        _ptr(status), _stream()), "norm_token_shift")
+    _count(1)
+
+
+def depth_average(results: torch.Tensor, coeff: torch.Tensor, n_terms: int, out: torch.Tensor,
+                  copy: Optional[torch.Tensor] = None) -> None:
+    """``out = sum_{j < n_terms} coeff[j] * results[j]`` (float32, terms added in order); ``copy`` gets the same rows."""
+    _need(results.dtype == torch.float32 and results.is_contiguous() and out.dtype == torch.float32 and out.is_contiguous()
+          and coeff.dtype == torch.float32 and coeff.numel() >= n_terms and results.shape[0] >= n_terms
+          and results[0].numel() == out.numel(), "depth_average: shapes and dtypes")
+    _need(copy is None or (copy.dtype == torch.float32 and copy.is_contiguous() and copy.numel() == out.numel()), "depth_average: copy")
+    check(library().pe_depth_average(_ptr(results), results.stride(0), _ptr(coeff), int(n_terms), _ptr(out), _ptr(copy),
+                                     out.numel(), _stream()), "depth_average")
+    _count(1)
+
+
+def polynorm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    """``coeff[0] N(z) + coeff[1] N(z^2) + coeff[2] N(z^3) + coeff[3]`` with ``N`` the division by a row's root mean square."""
+    _need(z.is_contiguous() and out.is_contiguous() and z.shape == out.shape and z.dtype == out.dtype
+          and coeff.dtype == torch.float32 and coeff.numel() == 4, "polynorm: shapes and dtypes")
+    check(library().pe_polynorm(dtype_tag(z.dtype), _ptr(z), _ptr(coeff), float(eps), _ptr(out), z.shape[0], z.shape[1],
+                                _stream()), "polynorm")
+    _count(1)
+
+
+def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, heads: int, dv: int) -> None:
+    """``x[t, h, :] *= sigmoid(g[t, h])`` when ``g`` has one column a head, ``x[t, c] *= sigmoid(g[t, c])`` otherwise."""
+    _need(x.stride(-1) == 1 and g.stride(-1) == 1 and x.dtype == g.dtype and x.shape[1] == heads * dv
+          and g.shape[1] in (heads, heads * dv) and g.shape[0] == x.shape[0], "sigmoid_gate: shapes and dtypes")
+    check(library().pe_sigmoid_gate(dtype_tag(x.dtype), _ptr(x), x.stride(0), _ptr(g), g.stride(0), x.shape[0], heads, dv,
+                                    1 if g.shape[1] == heads and dv != 1 else 0, _stream()), "sigmoid_gate")
+    _count(1)
+
+
+def diff_combine(a: torch.Tensor, out: torch.Tensor, heads: int, dv: int, lam: float, eps: float, post: float) -> None:
+    """``o = a[:, h] - lam * a[:, heads + h]``; ``out[:, h] = o / sqrt(mean(o^2) + eps) * post``."""
+    _need(a.is_contiguous() and out.is_contiguous() and a.dtype == torch.float32 and a.shape[1] == 2 * heads * dv
+          and out.shape[1] == heads * dv and a.shape[0] == out.shape[0], "diff_combine: shapes and dtypes")
+    check(library().pe_diff_combine(dtype_tag(out.dtype), _ptr(a), _ptr(out), a.shape[0], heads, dv, float(lam), float(eps),
+                                    float(post), _stream()), "diff_combine")
+    _count(1)
+
+
+def rows_to_pages(src: torch.Tensor, col0: int, heads: int, dim: int, token_seq: torch.Tensor, token_pos: torch.Tensor,
+                  seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, pages: torch.Tensor,
+                  status: torch.Tensor) -> None:
+    """Columns ``col0 .. col0 + heads * dim`` of every token's row into ``pages [num_pages, heads, 64, dim]`` at the
+    token's position in its sequence."""
+    _need(src.stride(-1) == 1 and pages.is_contiguous() and src.dtype == pages.dtype and col0 + heads * dim <= src.shape[1],
+          "rows_to_pages: shapes and dtypes")
+    check(library().pe_rows_to_pages(dtype_tag(src.dtype), _ptr(src), src.stride(0), int(col0), heads, dim, src.shape[0],
+                                     _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(page_table), page_table.shape[1],
+                                     num_pages, _ptr(pages), _ptr(status), _stream()), "rows_to_pages")
+    _count(1)
+
+
+def latent_prepare(x: torch.Tensor, q_col0: int, low_col0: int, heads: int, d: int, dr: int, rank: int, norm_w: torch.Tensor,
+                   eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, token_seq: torch.Tensor,
+                   token_pos: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
+                   pages: torch.Tensor, qfull: torch.Tensor, write_cache: bool, status: torch.Tensor) -> None:
+    """A latent-attention layer's cached rows ``[normed low-rank row | turned shared key part]`` into their pages, and the
+    turned part of every head's query into ``qfull [n, heads, rank + dr]`` (csrc/stream_parts.cu)."""
+    _need(x.stride(-1) == 1 and pages.is_contiguous() and qfull.is_contiguous() and x.dtype == pages.dtype == qfull.dtype
+          and norm_w.dtype == torch.float32 and norm_w.numel() == rank, "latent_prepare: shapes and dtypes")
+    if rot:
+        _need(cos is not None and cos.dtype == torch.float32 and cos.is_contiguous() and cos.shape == sin.shape
+              and cos.shape[1] * 2 == rot, "latent_prepare: angle tables float32 [rows, rot / 2]")
+    check(library().pe_latent_prepare(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(q_col0), int(low_col0), heads, d, dr, rank,
+                                      _ptr(norm_w), float(eps), _ptr(cos) if rot else None, _ptr(sin) if rot else None, int(rot),
+                                      cos.shape[0] if rot else 0, x.shape[0], _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot),
+                                      _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages), _ptr(qfull),
+                                      1 if write_cache else 0, _ptr(status), _stream()), "latent_prepare")
+    _count(1)

@@ -140,3 +140,60 @@ class ParallelBlock:
             deltas.append(self.ffn.forward(normed, ctx))
             scales.append(self.ffn_scale)
         return DeltaSum(deltas, scales)
+
+
+@register("arrangement", "sandwich_depth")
+class SandwichDepthBlock:
+    """A norm before and after each sublayer, a token shift on what the mixer reads, and an average over depth behind
+    the block:
+
+        y = x + post_mixer_norm(mixer(shift(mixer_norm(x))))
+        y = y + post_ffn_norm(ffn(ffn_norm(y)))                    (if the block has a feed-forward)
+        X_(i+1) = y ;   hand on  sum_{j <= i+1} coeff[j] X_j       (X_0: the embedding's output)
+
+    Parts by name: ``mixer_norm, shift, mixer, post_mixer_norm``, optionally ``ffn_norm, ffn, post_ffn_norm``, and
+    ``average``.  ``BlockSpec.params``: ``index`` (the block's number i) and ``depth`` (the number of blocks).  The
+    results X_j live in one float32 buffer of the step, ``[depth + 1, N, hidden]``; the block works in place on its own
+    row of it, and the averaging kernel writes the sum both to the stream and to the next block's row."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    def __init__(self, spec, parts, runtime) -> None:
+        self.runtime = runtime
+        self.name = spec.name
+        self.index = int(spec.params["index"])
+        self.depth = int(spec.params["depth"])
+        self.mixer_norm, self.shift, self.mixer = parts["mixer_norm"], parts["shift"], parts["mixer"]
+        self.post_mixer_norm = parts["post_mixer_norm"]
+        self.ffn = parts.get("ffn")
+        self.ffn_norm, self.post_ffn_norm = parts.get("ffn_norm"), parts.get("post_ffn_norm")
+        self.average = parts["average"]
+
+    def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
+        rt = self.runtime
+        if pending is not None:       # a block of another arrangement before this one left its last delta to be added
+            if isinstance(pending, DeltaSum):
+                pending.add_into(stream, stream)
+            else:
+                stream.add_(pending)
+        n, hidden = stream.shape
+        results = ctx.buffer("depth.results", (self.depth + 1, n, hidden), torch.float32)
+        work = results[self.index + 1]
+        if self.index == 0 or getattr(ctx, "depth_rows_ready", None) != self.index + 1:
+            # the first block of a step (or one that follows a block of another arrangement) starts the rows itself
+            if self.index == 0:
+                results[0].copy_(stream)
+            work.copy_(stream)
+        normed = ctx.buffer("block.normed", (n, hidden), rt.dtype)
+        self.shift.norm_forward(work, self.mixer_norm, normed, ctx, view["shift"])
+        mview = view["mixer"]
+        mixed = self.mixer.forward(normed, ctx, mview) if writes_cache else self.mixer.forward(normed, ctx, mview, writes_cache=False)
+        self.post_mixer_norm.add_after(work, mixed, None)
+        if self.ffn is not None:
+            self.ffn_norm.add_forward(work, None, normed)
+            self.post_ffn_norm.add_after(work, self.ffn.forward(normed, ctx), None)
+        last = self.index + 1 >= self.depth
+        self.average.forward(results, stream, None if last else results[self.index + 2])
+        ctx.depth_rows_ready = None if last else self.index + 2
+        ctx.stream_copy = None
+        return None

@@ -1,0 +1,117 @@
+"""Differential attention: every head takes two softmax maps over the same values and subtracts the second.
+
+For a token with input ``h`` (W stored [out, in]; q and k rows laid out head by head as [map 1 | map 2]):
+
+    q = W_q h   heads x 2 x d        k = W_k h   kv_heads x 2 x d        v = W_v h   kv_heads x dv
+    a_m   = softmax_j(scale * q_(head, m) . k_(head / group, m)(j)) v_(head / group)(j)        m = 1, 2, over visible j
+    o     = a_1 - lambda * a_2 ;   o <- o / sqrt(mean(o^2) + eps) * (1 - diff)     per head, no weight
+    lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff                                one number for the layer
+    out   = W_o o
+
+Visible keys: j <= i, and with ``chunk`` only those of the query's own block of ``chunk`` positions (blocks counted from
+the sequence's start).  A layer with ``shared_kv`` has no k and v projections: it reads the cache entry of another layer
+(the plan's ``RunStep`` says which) with its own queries and mask.
+
+The two maps run as one grouped-query attention: the projections' rows are reordered at load time to [map][head], so
+the first map's heads come first, query head ``m * heads + h`` reads key head ``m * kv_heads + h / group`` (the usual
+mapping), and key head g reads value head ``g % kv_heads``; the cache keeps ``2 * kv_heads`` key heads and ``kv_heads`` value
+heads per position.  Scores, softmax, the subtraction and the norm are float32 in every run dtype.
+"""
+from __future__ import annotations
+
+import math
+from typing import Dict, Optional
+
+import torch
+
+from ..kernels import ops
+from .attention import SPLIT_KEYS
+from .linear import fuse_rows
+from .registry import register
+from .spec import CacheRequest, WeightDecl
+
+
+def maps_first(w: torch.Tensor, heads: int, d: int) -> torch.Tensor:
+    """Rows [head][map][d] of a projection reordered to [map][head][d]."""
+    return w.view(heads, 2, d, w.shape[1]).transpose(0, 1).reshape(2 * heads * d, w.shape[1]).contiguous()
+
+
+@register("mixer", "diff_attention")
+class DiffAttention:
+    """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``v_head_dim``, ``scale``, ``diff``, ``eps``, ``chunk``
+    (None: every earlier key), ``cache_chunk`` (what the cache may drop: the chunk that every reader of this layer's keys
+    shares, or None), ``shared_kv`` (true: no k and v projections).  weights: ``q_proj [heads*2*d, hidden]``, ``k_proj
+    [kv_heads*2*d, hidden]``, ``v_proj [kv_heads*dv, hidden]``, ``lq1, lk1, lq2, lk2 [d]``, ``o_proj [hidden, heads*dv]``."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def sizes(cls, params):
+        return (int(params["hidden"]), int(params["n_heads"]), int(params["n_kv_heads"]), int(params["head_dim"]),
+                int(params.get("v_head_dim") or params["head_dim"]))
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        h, nh, nkv, d, dv = cls.sizes(params)
+        decls = {"q_proj": WeightDecl((nh * 2 * d, h)), "o_proj": WeightDecl((h, nh * dv))}
+        if not params.get("shared_kv"):
+            decls["k_proj"] = WeightDecl((nkv * 2 * d, h))
+            decls["v_proj"] = WeightDecl((nkv * dv, h))
+        for name in ("lq1", "lk1", "lq2", "lk2"):
+            decls[name] = WeightDecl((d,))
+        return decls
+
+    @classmethod
+    def cache_request(cls, params) -> Optional[CacheRequest]:
+        _, _, nkv, d, dv = cls.sizes(params)
+        return CacheRequest(kind="kv", kv_heads=2 * nkv, head_dim=d, v_head_dim=dv, value_heads=nkv,
+                            chunk=params.get("cache_chunk") or None)
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.hidden, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim = self.sizes(params)
+        nh, nkv, d, dv = self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim
+        if nh % nkv:
+            raise ValueError("n_heads must be a multiple of n_kv_heads")
+        if d > 512 or dv > 512:
+            raise ValueError(f"head_dim {d} / v_head_dim {dv} is beyond what the attention kernels take (<= 512)")
+        self.scale = float(params["scale"])
+        self.diff = float(params["diff"])
+        self.eps = float(params.get("eps", 1e-6))
+        self.chunk = int(params["chunk"]) if params.get("chunk") else 0
+        self.shared_kv = bool(params.get("shared_kv"))
+        mats = [maps_first(weights["q_proj"], nh, d)]
+        if not self.shared_kv:
+            mats += [maps_first(weights["k_proj"], nkv, d), weights["v_proj"]]
+        self.qkv = fuse_rows(runtime, mats)
+        self.q_cols, self.k_cols, self.v_cols = 2 * nh * d, 2 * nkv * d, nkv * dv
+        self.o_proj = runtime.adopt(weights["o_proj"])
+        f = lambda name: weights[name].to(torch.float32)
+        # one number for the layer, from float32 sums
+        self.lam = (math.exp(float((f("lq1") * f("lk1")).sum())) - math.exp(float((f("lq2") * f("lk2")).sum())) + self.diff)
+
+    def forward(self, x: torch.Tensor, ctx, view, writes_cache: bool = True) -> torch.Tensor:
+        rt = self.runtime
+        n, nh, nkv, d, dv = x.shape[0], self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim
+        if writes_cache and self.shared_kv:
+            raise ValueError("a differential-attention layer without k and v projections reads another layer's cache entry")
+        qkv = ctx.buffer("diff.qkv", (n, self.qkv.shape[0]), rt.dtype)
+        rt.linear(x, self.qkv, out=qkv)
+        where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages)
+        if writes_cache:
+            ops.rows_to_pages(qkv, self.q_cols, 2 * nkv, d, *where, view.k_pages, rt.status)
+            ops.rows_to_pages(qkv, self.q_cols + self.k_cols, nkv, dv, *where, view.v_pages, rt.status)
+        maps = ctx.buffer("diff.maps", (n, 2 * nh * dv), torch.float32)   # the two maps stay float32 up to their difference
+        scratch, max_splits = None, 0
+        if ctx.decode:
+            max_splits = ctx.max_splits(SPLIT_KEYS)
+            scratch = ctx.buffer("attn.scratch", (ops.attention_generic_scratch_floats(ctx.n_seqs, 2 * nh, dv, max_splits),),
+                                 torch.float32)
+        ops.attention_generic_masked(ctx.decode, qkv, maps, ctx.n_seqs, ctx.max_q, 2 * nh, 2 * nkv, d, dv, self.scale,
+                                     ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
+                                     view.v_pages, scratch, SPLIT_KEYS, max_splits, rt.status, chunk=self.chunk, v_heads=nkv)
+        heads = ctx.buffer("diff.heads", (n, nh * dv), rt.dtype)
+        ops.diff_combine(maps, heads, nh, dv, self.lam, self.eps, 1.0 - self.diff)
+        delta = ctx.buffer("diff.delta", (n, self.hidden), rt.dtype)
+        rt.linear(heads, self.o_proj, out=delta)
+        return delta

@@ -6,6 +6,9 @@ that return their input, optionally with a shared expert that every token passes
     y = sum_chosen s_e * expert_e(h)  (+ shared(h)) ;  expert_e(h) = h for e >= n_experts (identity experts)
     expert(h) = D act(G h, U h)  with the activations of ``parts/swiglu.py``
 
+With ``choice = "top_logits"`` the router instead takes the ``top`` largest of ``z + bias`` and weights them by a softmax
+over the chosen ones alone (no correction).
+
 The (token, choice) pairs are grouped by expert on the device and every expert's rows go through its matrices in one
 launch per product, so nothing is read back to the host and a decode step stays recordable.  A handful of pairs (a
 decode step) and every float32 run use the package's own kernel, which streams an expert's weights once per eight
@@ -33,7 +36,10 @@ LIBRARY_ROWS = 64
 class RoutedExperts:
     """params: ``hidden``, ``n_experts``, ``n_identity`` (router outputs beyond the real experts), ``top``, ``intermediate``,
     ``activation`` / ``limit`` / ``alpha`` (of every expert), ``shared`` (None, or the params of a ``swiglu`` part).
-    weights: ``router [n_experts + n_identity, hidden]``, ``correction [n_experts + n_identity]``, ``e<i>.gate, e<i>.up
+    ``choice`` ("softmax_all", the default: softmax over every output, the choice moved by ``correction``, weights not
+    renormalised; "top_logits": the largest of ``z + router_bias``, softmax over the chosen).
+    weights: ``router [n_experts + n_identity, hidden]``, ``correction [n_experts + n_identity]`` (softmax_all) or
+    ``router_bias [n_experts + n_identity]`` (top_logits), ``e<i>.gate, e<i>.up
     [I, H]``, ``e<i>.down [H, I]``, and ``shared.gate, shared.up, shared.down`` with a shared expert."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
@@ -41,7 +47,8 @@ class RoutedExperts:
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         h, n, extra, inter = (int(params[k]) for k in ("hidden", "n_experts", "n_identity", "intermediate"))
-        decls = {"router": WeightDecl((n + extra, h)), "correction": WeightDecl((n + extra,))}
+        decls = {"router": WeightDecl((n + extra, h))}
+        decls["router_bias" if params.get("choice") == "top_logits" else "correction"] = WeightDecl((n + extra,))
         for e in range(n):
             decls[f"e{e}.gate"] = WeightDecl((inter, h))
             decls[f"e{e}.up"] = WeightDecl((inter, h))
@@ -66,7 +73,14 @@ class RoutedExperts:
         self.alpha = float(params.get("alpha") or 1.0)
         dev, dt = runtime.device, runtime.dtype
         self.router = runtime.adopt(weights["router"])
-        self.correction = runtime.adopt(weights["correction"], torch.float32)
+        self.choice = str(params.get("choice") or "softmax_all")
+        if self.choice not in ("softmax_all", "top_logits"):
+            raise ValueError(f"router choice {self.choice!r} is not built ('softmax_all' and 'top_logits' are)")
+        self.correction = self.router_bias = None
+        if self.choice == "top_logits":
+            self.router_bias = runtime.adopt(weights["router_bias"], torch.float32)
+        else:
+            self.correction = runtime.adopt(weights["correction"], torch.float32)
         if self.n_experts:
             self.gate_up = torch.stack([torch.cat([weights[f"e{e}.gate"], weights[f"e{e}.up"]]).to(device=dev, dtype=dt)
                                         for e in range(self.n_experts)]).contiguous()
@@ -93,11 +107,17 @@ class RoutedExperts:
         return (self.hidden % 16 == 0 and self.intermediate % 8 == 0
                 and ops.gemm_smallm_supported(x, self.gate_up.view(-1, self.hidden)))
 
+    def route(self, logits, chosen, weight, dense_rows=None, n_real: int = 0) -> None:
+        if self.choice == "top_logits":
+            ops.moe_route_logits(logits, self.router_bias, self.top, chosen, weight, dense_rows, n_real)
+        else:
+            ops.moe_route(logits, self.correction, self.top, chosen, weight, dense_rows, n_real)
+
     def forward_every_expert(self, x, ctx, logits, chosen, weight) -> torch.Tensor:
         rt = self.runtime
         n, E, ff = x.shape[0], self.n_experts, self.intermediate
         pair_row = ctx.buffer("moe.pair_row", (n, self.top), torch.int32)
-        ops.moe_route(logits, self.correction, self.top, chosen, weight, pair_row, E)
+        self.route(logits, chosen, weight, pair_row, E)
         gu = ctx.buffer("moe.every_gu", (n, E * 2 * ff), rt.dtype)
         ops.gemm_smallm(x, self.gate_up.view(E * 2 * ff, self.hidden), gu)
         act = ctx.buffer("moe.every_act", (n * E, ff), rt.dtype)
@@ -121,7 +141,7 @@ class RoutedExperts:
         weight = ctx.buffer("moe.weight", (n, top), torch.float32)
         if self.runs_every_expert(x, n):
             return self.forward_every_expert(x, ctx, logits, chosen, weight)
-        ops.moe_route(logits, self.correction, top, chosen, weight)
+        self.route(logits, chosen, weight)
         offsets = ctx.buffer("moe.offsets", (self.n_experts + 1,), torch.int32)
         row_token = ctx.buffer("moe.row_token", (n * top,), torch.int32)
         pair_row = ctx.buffer("moe.pair_row", (n, top), torch.int32)

@@ -13,19 +13,22 @@ from .spec import WeightDecl
 
 @register("norm", "rmsnorm")
 class RMSNorm:
-    """params: ``dim``, ``eps``.  weights: ``weight [dim]`` (kept in float32)."""
+    """params: ``dim``, ``eps``, optionally ``offset`` (the stored weight is the distance from it: the norm multiplies by
+    ``offset + weight``; random weights then lie around zero).  weights: ``weight [dim]`` (kept in float32)."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
-        return {"weight": WeightDecl((int(params["dim"]),), "norm")}
+        return {"weight": WeightDecl((int(params["dim"]),), "matrix" if params.get("offset") else "norm")}
 
     def __init__(self, params, weights, runtime) -> None:
         self.dim = int(params["dim"])
         self.eps = float(params["eps"])
         self.runtime = runtime
         self.weight = runtime.adopt(weights["weight"], torch.float32)
+        if params.get("offset"):
+            self.weight = (self.weight + float(params["offset"])).contiguous()
 
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:

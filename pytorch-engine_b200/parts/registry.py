@@ -21,6 +21,9 @@ the loader read them, on the run device):
 * feed_forward: ``forward(x, ctx) -> delta``.
 * embedding:    ``forward(token_ids_i32) -> residual stream float32 [N, hidden]``.
 * head:         ``forward(x) -> logits float32 [rows, vocab]``.
+* stream:       a part that an arrangement applies to the stream itself or to what a sublayer reads (a token shift,
+                an average over the blocks' results); it may have ``cache_request(params)`` like a mixer, and its
+                methods are whatever the arrangement that names it calls.
 * arrangement:  a class ``(block_spec, parts, runtime)`` with
                 ``forward(stream, pending, ctx, cache_view) -> pending``.
 """
@@ -28,7 +31,7 @@ from __future__ import annotations
 
 from typing import Dict
 
-ROLES = ("norm", "position", "mixer", "feed_forward", "embedding", "head", "arrangement")
+ROLES = ("norm", "position", "mixer", "feed_forward", "embedding", "head", "arrangement", "stream")
 _REGISTRIES: Dict[str, Dict[str, type]] = {role: {} for role in ROLES}
 
 

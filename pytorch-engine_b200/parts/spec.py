@@ -54,6 +54,11 @@ class BlockSpec:
         """Names of the parts that are mixers, in the order the block lists them."""
         return tuple(n for n, (role, _) in self.parts.items() if role == "mixer")
 
+    def keeper_names(self) -> Tuple[str, ...]:
+        """Names of the parts that may keep something per sequence: the mixers, and the parts of role "stream" (a
+        token shift keeps the previous token's input), in the order the block lists them."""
+        return tuple(n for n, (role, _) in self.parts.items() if role in ("mixer", "stream"))
+
 
 @dataclass(frozen=True)
 class RunStep:
@@ -64,10 +69,21 @@ class RunStep:
     block: int
     cache: Optional[int] = None
     writes_cache: bool = True
+    # the names of the block's parts that ``cache`` and ``writes_cache`` apply to; empty: all of them.  A part that is
+    # not named keeps an entry of its own and writes it (a block that reads another block's keys and values while its
+    # token shift keeps a row of its own).
+    shared: Tuple[str, ...] = ()
 
     @property
     def cache_entry(self) -> int:
         return self.block if self.cache is None else self.cache
+
+    def entry_of(self, part_name: str) -> int:
+        """The cache entry that the block's part ``part_name`` uses in this run."""
+        return self.cache_entry if (not self.shared or part_name in self.shared) else self.block
+
+    def writes(self, part_name: str) -> bool:
+        return self.writes_cache or bool(self.shared and part_name not in self.shared)
 
 
 @dataclass(frozen=True)
@@ -126,7 +142,10 @@ class CacheRequest:
 
     ``kind`` "kv": keys and values of every position, ``kv_heads x head_dim`` each (values
     ``kv_heads x v_head_dim`` when that is given and differs), and with ``window`` only the last
-    ``window`` positions need to stay.  ``kind`` "state": tensors of fixed
+    ``window`` positions need to stay; with ``chunk`` only the positions of the block of ``chunk`` positions that
+    the next query falls into.  ``value_heads``: the values have that many heads instead of ``kv_heads`` (several
+    key maps over one set of values).  ``values_in_keys``: no values are stored; the mixer reads them out of the key
+    rows (a latent cache whose row is both).  ``kind`` "state": tensors of fixed
     shape per sequence (``state_shapes``: name -> (shape, torch dtype name)), zero when a
     sequence starts.  Entries with equal requests share one group of storage.
     """
@@ -137,10 +156,18 @@ class CacheRequest:
     window: Optional[int] = None
     state_shapes: Tuple[Tuple[str, Tuple[int, ...], str], ...] = ()
     v_head_dim: Optional[int] = None
+    chunk: Optional[int] = None
+    value_heads: Optional[int] = None
+    values_in_keys: bool = False
 
     @property
     def value_dim(self) -> int:
         return self.head_dim if self.v_head_dim is None else self.v_head_dim
 
+    @property
+    def n_value_heads(self) -> int:
+        return self.kv_heads if self.value_heads is None else self.value_heads
+
     def group_key(self):
-        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shapes, self.value_dim)
+        return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shapes, self.value_dim, self.chunk,
+                self.n_value_heads, self.values_in_keys)
