@@ -2,4 +2,4 @@
 parts and registers itself under the name that ``config.json`` carries in ``architectures[0]``."""
 from . import lunadra, qwen3, vabelorn, vemepel  # noqa: F401
 
-__all__ = ["lunadra", "qwen3", "vabelorn"]
+__all__ = ["lunadra", "qwen3", "vabelorn", "vemepel"]

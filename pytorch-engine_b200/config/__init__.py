@@ -10,6 +10,6 @@ from .vemepel import VemepelConfig
 
 __all__ = [
     "ConfigError", "ModelConfig", "read_config_dict", "Architecture", "architecture", "architecture_names",
-    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig", "LunadraConfig",
+    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig", "LunadraConfig", "VemepelConfig",
     "preset", "preset_names", "register_preset_folder", "unregister_preset_folder",
 ]

@@ -69,8 +69,8 @@ int pe_depth_average(const float* results, long long layer_stride, const float* 
     float* copy, long long n, cudaStream_t stream);
 int pe_polynorm(int dtype, const void* z, const float* coeff, float eps, void* out, int n_rows, int width,
     cudaStream_t stream);
-int pe_sigmoid_gate(int dtype, void* x, long long x_ld, const void* g, long long g_ld, int n_tokens, int heads, int dv,
-    int per_head, cudaStream_t stream);
+int pe_sigmoid_gate(int dtype, const void* x, long long x_head_stride, long long x_token_stride, const void* g,
+    long long g_ld, void* out, long long out_ld, int n_tokens, int heads, int dv, int per_head, cudaStream_t stream);
 int pe_diff_combine(int dtype, const float* a, void* out, int n_tokens, int heads, int dv, float lambda, float eps,
     float post, cudaStream_t stream);
 int pe_rows_to_pages(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int n_tokens,
@@ -79,7 +79,8 @@ int pe_rows_to_pages(int dtype, const void* src, long long src_ld, int col0, int
 int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q_col0, int low_col0, int heads, int d, int dr,
     int rank, const float* norm_w, float eps, const float* cos_t, const float* sin_t, int rot, int table_rows,
     int n_tokens, const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table,
-    int table_stride, int num_pages, void* pages, void* qfull, int write_cache, int* status, cudaStream_t stream);
+    int table_stride, int num_pages, void* pages, void* qfull, const void* absorbed, int write_cache, int* status,
+    cudaStream_t stream);
 
 // embedding.cu
 int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,

@@ -96,18 +96,21 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const T* z, const float* 
   }
 }
 
+// x: feature c of head h of token t at x + h * x_head_stride + t * x_token_stride + c (heads side by side in a row, or
+// one matrix a head as a product over heads leaves them); out: packed rows [n, heads * dv].
 template <typename T>
-__global__ void sigmoid_gate_kernel(T* x, long long x_ld, const T* g, long long g_ld, int n_tokens, int heads, int dv,
-                                    int per_head) {
+__global__ void sigmoid_gate_kernel(const T* x, long long x_head_stride, long long x_token_stride, const T* g, long long g_ld,
+                                    T* __restrict__ out, long long out_ld, int n_tokens, int heads, int dv, int per_head) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int row = heads * dv;
   const size_t total = (size_t)n_tokens * row;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
     const int t = (int)(i / row), c = (int)(i - (size_t)t * row);
-    const float z = to_f32<T>(g[(size_t)t * g_ld + (per_head ? c / dv : c)]);
-    T* p = x + (size_t)t * x_ld + c;
-    *p = from_f32<T>(to_f32<T>(*p) / (1.f + expf(-z)));
+    const int h = c / dv;
+    const float z = to_f32<T>(g[(size_t)t * g_ld + (per_head ? h : c)]);
+    const float v = to_f32<T>(x[(size_t)h * x_head_stride + (size_t)t * x_token_stride + (c - h * dv)]);
+    out[(size_t)t * out_ld + c] = from_f32<T>(v / (1.f + expf(-z)));
   }
 }
 
@@ -171,7 +174,7 @@ __global__ void rows_to_pages_kernel(const T* src, long long src_ld, int col0, i
 // A latent-attention layer's step, per token (grid: tokens).  x row: [.. q: heads x (d + dr) at q_col0 ..
 // low: rank + dr at low_col0 ..].
 //   cached row  = [ low[:rank] / rms(low[:rank]) * norm_w | turn(low[rank:]) ]        -> pages [num_pages, 1, 64, rank + dr]
-//   qfull[t, h] = [ (left as it is: the absorbed query is written by a product) | turn(q[h, d:]) ]   [n, heads, rank + dr]
+//   qfull[t, h] = [ absorbed[h, t] (a product over heads left it as [heads, n, rank]; null: left as it is) | turn(q[h, d:]) ]
 // turn: adjacent pairs (2i, 2i+1) of the first `rot` features by the angle tables' row of the token's position.
 template <typename T>
 __global__ void __launch_bounds__(256) latent_prepare_kernel(const T* x, long long x_ld, int q_col0, int low_col0, int heads,
@@ -180,8 +183,8 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const T* x, long lo
                                                              const float* __restrict__ sin_t, int rot, int table_rows,
                                                              const int* token_seq, const int* token_pos, const int* seq_slot,
                                                              const int* page_table, int table_stride, int num_pages,
-                                                             T* __restrict__ pages, T* __restrict__ qfull, int write_cache,
-                                                             int* status) {
+                                                             T* __restrict__ pages, T* __restrict__ qfull,
+                                                             const T* absorbed, int n_tokens, int write_cache, int* status) {
   __shared__ float red[32];
   pdl_wait_block();
   pdl_launch_dependents();
@@ -207,6 +210,12 @@ __global__ void __launch_bounds__(256) latent_prepare_kernel(const T* x, long lo
       v = (c & 1) ? fmaf(v, cs[m], o * sn[m]) : fmaf(v, cs[m], -o * sn[m]);
     }
     qfull[((size_t)t * heads + h) * wide + rank + c] = from_f32<T>(v);
+  }
+  if (absorbed) {
+    for (int i = threadIdx.x; i < heads * rank; i += blockDim.x) {
+      const int h = i / rank, c = i - h * rank;
+      qfull[((size_t)t * heads + h) * wide + c] = absorbed[((size_t)h * n_tokens + t) * rank + c];
+    }
   }
   if (!write_cache) return;
   const T* low = row + low_col0;
@@ -275,13 +284,14 @@ extern "C" int pe_polynorm(int dtype, const void* z, const float* coeff, float e
   return PE_OK;
 }
 
-extern "C" int pe_sigmoid_gate(int dtype, void* x, long long x_ld, const void* g, long long g_ld, int n_tokens, int heads,
-                               int dv, int per_head, cudaStream_t stream) {
+extern "C" int pe_sigmoid_gate(int dtype, const void* x, long long x_head_stride, long long x_token_stride, const void* g,
+                               long long g_ld, void* out, long long out_ld, int n_tokens, int heads, int dv, int per_head,
+                               cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (heads <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
   const int blocks = pe::flat_blocks((size_t)n_tokens * heads * dv, 256);
-  PE_BY_DTYPE(dtype, pe::launch(pe::sigmoid_gate_kernel<T>, blocks, 256, 0, stream, (T*)x, x_ld, (const T*)g, g_ld, n_tokens,
-                                heads, dv, per_head));
+  PE_BY_DTYPE(dtype, pe::launch(pe::sigmoid_gate_kernel<T>, blocks, 256, 0, stream, (const T*)x, x_head_stride, x_token_stride,
+                                (const T*)g, g_ld, (T*)out, out_ld, n_tokens, heads, dv, per_head));
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -313,13 +323,14 @@ extern "C" int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q
                                  int rank, const float* norm_w, float eps, const float* cos_t, const float* sin_t, int rot,
                                  int table_rows, int n_tokens, const int* token_seq, const int* token_pos,
                                  const int* seq_slot, const int* page_table, int table_stride, int num_pages, void* pages,
-                                 void* qfull, int write_cache, int* status, cudaStream_t stream) {
+                                 void* qfull, const void* absorbed, int write_cache, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (heads <= 0 || d <= 0 || dr < 0 || rank <= 0 || rot < 0 || rot > dr || (rot & 1)) return PE_ERR_BAD_ARGUMENT;
   if (rot > 0 && (!cos_t || !sin_t)) return PE_ERR_BAD_ARGUMENT;
   PE_BY_DTYPE(dtype, pe::launch(pe::latent_prepare_kernel<T>, n_tokens, 256, 0, stream, (const T*)x, x_ld, q_col0, low_col0,
                                 heads, d, dr, rank, norm_w, eps, cos_t, sin_t, rot, table_rows, token_seq, token_pos, seq_slot,
-                                page_table, table_stride, num_pages, (T*)pages, (T*)qfull, write_cache, status));
+                                page_table, table_stride, num_pages, (T*)pages, (T*)qfull, (const T*)absorbed, n_tokens,
+                                write_cache, status));
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -91,10 +91,10 @@ _SIGNATURES = {
     "pe_norm_token_shift": [I, P, P, F, P, P, P, P, P, P, I, I, I, P, P],
     "pe_depth_average": [P, L, P, I, P, P, L, P],
     "pe_polynorm": [I, P, P, F, P, I, I, P],
-    "pe_sigmoid_gate": [I, P, L, P, L, I, I, I, I, P],
+    "pe_sigmoid_gate": [I, P, L, L, P, L, P, L, I, I, I, I, P],
     "pe_diff_combine": [I, P, P, I, I, I, F, F, F, P],
     "pe_rows_to_pages": [I, P, L, I, I, I, I, P, P, P, P, I, I, P, P, P],
-    "pe_latent_prepare": [I, P, L, I, I, I, I, I, I, P, F, P, P, I, I, I, P, P, P, P, I, I, P, P, I, P, P],
+    "pe_latent_prepare": [I, P, L, I, I, I, I, I, I, P, F, P, P, I, I, I, P, P, P, P, I, I, P, P, P, I, P, P],
 }
 _RESTYPES = {"pe_wait_limit_polls": (L, []),
              "pe_attention_generic_scratch_floats": (L, [I, I, I, I]),

@@ -794,12 +794,17 @@ def polynorm(z: torch.Tensor, coeff: torch.Tensor, eps: float, out: torch.Tensor
     _count(1)
 
 
-def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, heads: int, dv: int) -> None:
-    """``x[t, h, :] *= sigmoid(g[t, h])`` when ``g`` has one column a head, ``x[t, c] *= sigmoid(g[t, c])`` otherwise."""
-    _need(x.stride(-1) == 1 and g.stride(-1) == 1 and x.dtype == g.dtype and x.shape[1] == heads * dv
-          and g.shape[1] in (heads, heads * dv) and g.shape[0] == x.shape[0], "sigmoid_gate: shapes and dtypes")
-    check(library().pe_sigmoid_gate(dtype_tag(x.dtype), _ptr(x), x.stride(0), _ptr(g), g.stride(0), x.shape[0], heads, dv,
-                                    1 if g.shape[1] == heads and dv != 1 else 0, _stream()), "sigmoid_gate")
+def sigmoid_gate(x: torch.Tensor, g: torch.Tensor, out: torch.Tensor) -> None:
+    """``out[t, h, :] = x[h, t, :] * sigmoid(g[t, h])`` when ``g`` has one column a head, ``* sigmoid(g[t, h, :])`` when it has
+    one a feature.  ``x [heads, n, dv]`` with any head and token strides (a product over heads leaves one matrix a head; a
+    transposed view of packed rows works too); ``out [n, heads * dv]``."""
+    heads, n, dv = x.shape
+    _need(x.stride(-1) == 1 and g.stride(-1) == 1 and out.stride(-1) == 1 and x.dtype == g.dtype == out.dtype
+          and tuple(out.shape) == (n, heads * dv) and g.shape[1] in (heads, heads * dv) and g.shape[0] == n,
+          "sigmoid_gate: shapes and dtypes")
+    check(library().pe_sigmoid_gate(dtype_tag(x.dtype), _ptr(x), x.stride(0), x.stride(1), _ptr(g), g.stride(0), _ptr(out),
+                                    out.stride(0), n, heads, dv, 1 if g.shape[1] == heads and dv != 1 else 0, _stream()),
+          "sigmoid_gate")
     _count(1)
 
 
@@ -828,9 +833,13 @@ def rows_to_pages(src: torch.Tensor, col0: int, heads: int, dim: int, token_seq:
 def latent_prepare(x: torch.Tensor, q_col0: int, low_col0: int, heads: int, d: int, dr: int, rank: int, norm_w: torch.Tensor,
                    eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, token_seq: torch.Tensor,
                    token_pos: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
-                   pages: torch.Tensor, qfull: torch.Tensor, write_cache: bool, status: torch.Tensor) -> None:
+                   pages: torch.Tensor, qfull: torch.Tensor, write_cache: bool, status: torch.Tensor,
+                   absorbed: Optional[torch.Tensor] = None) -> None:
     """A latent-attention layer's cached rows ``[normed low-rank row | turned shared key part]`` into their pages, and the
-    turned part of every head's query into ``qfull [n, heads, rank + dr]`` (csrc/stream_parts.cu)."""
+    turned part of every head's query into ``qfull [n, heads, rank + dr]``; ``absorbed [heads, n, rank]``, if given, fills
+    the leading features of ``qfull``'s rows (csrc/stream_parts.cu)."""
+    _need(absorbed is None or (absorbed.is_contiguous() and absorbed.dtype == x.dtype
+                               and tuple(absorbed.shape) == (heads, x.shape[0], rank)), "latent_prepare: absorbed [heads, n, rank]")
     _need(x.stride(-1) == 1 and pages.is_contiguous() and qfull.is_contiguous() and x.dtype == pages.dtype == qfull.dtype
           and norm_w.dtype == torch.float32 and norm_w.numel() == rank, "latent_prepare: shapes and dtypes")
     if rot:
@@ -839,6 +848,6 @@ def latent_prepare(x: torch.Tensor, q_col0: int, low_col0: int, heads: int, d: i
     check(library().pe_latent_prepare(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(q_col0), int(low_col0), heads, d, dr, rank,
                                       _ptr(norm_w), float(eps), _ptr(cos) if rot else None, _ptr(sin) if rot else None, int(rot),
                                       cos.shape[0] if rot else 0, x.shape[0], _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot),
-                                      _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages), _ptr(qfull),
+                                      _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages), _ptr(qfull), _ptr(absorbed),
                                       1 if write_cache else 0, _ptr(status), _stream()), "latent_prepare")
     _count(1)

@@ -110,13 +110,14 @@ class LatentAttention:
         if self.rot:
             cos, sin, _ = self.position.tables()
         pages = view.k_pages
-        ops.latent_prepare(qlg, 0, self.low_col0, nh, d, dr, r, self.norm_w, self.eps, cos, sin, self.rot, ctx.token_seq,
-                           ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages, pages, qfull, writes_cache, rt.status)
-        # the absorbed queries, head by head: [heads, n, d] x [heads, d, rank] into the leading features of qfull's rows
+        # the absorbed queries, head by head: [heads, n, d] x [heads, d, rank]
         q_heads = qlg[:, :self.q_cols].view(n, nh, d + dr)[:, :, :d].transpose(0, 1)
         absorbed = ctx.buffer("latent.absorbed", (nh, n, r), rt.dtype)
         rt.batched_linear(q_heads, self.uk.transpose(1, 2), absorbed)
-        qfull[:, :, :r].copy_(absorbed.transpose(0, 1))
+        # the cached rows into their pages; the queries' rows put together: [absorbed | turned part]
+        ops.latent_prepare(qlg, 0, self.low_col0, nh, d, dr, r, self.norm_w, self.eps, cos, sin, self.rot, ctx.token_seq,
+                           ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages, pages, qfull, writes_cache, rt.status,
+                           absorbed=absorbed)
         mixed = ctx.buffer("latent.mixed", (n, nh, r), rt.dtype)
         scratch, max_splits = None, 0
         if ctx.decode:
@@ -130,8 +131,7 @@ class LatentAttention:
         heads_t = ctx.buffer("latent.heads_t", (nh, n, dv), rt.dtype)
         rt.batched_linear(mixed.transpose(0, 1), self.uv_t.transpose(1, 2), heads_t)
         heads = ctx.buffer("latent.heads", (n, nh * dv), rt.dtype)
-        heads.view(n, nh, dv).copy_(heads_t.transpose(0, 1))
-        ops.sigmoid_gate(heads, qlg[:, self.gate_col0:self.gate_col0 + self.gate_rows], nh, dv)
+        ops.sigmoid_gate(heads_t, qlg[:, self.gate_col0:self.gate_col0 + self.gate_rows], heads)
         delta = ctx.buffer("latent.delta", (n, self.hidden), rt.dtype)
         rt.linear(heads, self.o_proj, out=delta)
         return delta

@@ -226,3 +226,92 @@ class PlainVemepel:
         state["length"] = past + T
         logits = st(norm_around_zero(x, w["final.norm"], eps)) @ w["head"].T * float(self.cfg["logit_scale"])
         return (logits, torch.stack(after)) if trace else logits
+
+
+# ---- helpers of the tests: tensor shapes from the configuration, random weights, whole runs ----------------------------
+def tensor_shapes(config: dict) -> Dict[str, tuple]:
+    """Name -> shape of every tensor that a model of ``config`` holds."""
+    W, V = int(config["width"]), int(config["vocab"])
+    out = {"embed": (V, W), "final.norm": (W,), "head": (V, W)}
+    for i, layer in enumerate(config["layers"]):
+        p, m = f"l{i}.", layer["mixer"]
+        for n in ("norm1", "norm1b", "shift"):
+            out[p + n] = (W,)
+        out[p + "dwa"] = (i + 2,)
+        H, d, dv = int(m["heads"]), int(m["dim"]), int(m.get("vdim", m["dim"]))
+        if layer["type"] == "attention":
+            G = int(m.get("kv_heads", H))
+            out[p + "mix.q"] = (H * 2 * d, W)
+            if m.get("kv_from") is None:
+                out[p + "mix.k"] = (G * 2 * d, W)
+                out[p + "mix.v"] = (G * dv, W)
+            for n in ("lq1", "lk1", "lq2", "lk2"):
+                out[p + "mix." + n] = (d,)
+        else:
+            r, dr = int(m["kv_rank"]), int(m.get("rot_dim", 0) or 0)
+            out[p + "mix.q"] = (H * (d + dr), W)
+            out[p + "mix.dkv"] = (r + dr, W)
+            out[p + "mix.dkv.norm"] = (r,)
+            out[p + "mix.uk"] = (H * d, r)
+            out[p + "mix.uv"] = (H * dv, r)
+            out[p + "mix.g"] = (H * dv if dr else H, W)
+        out[p + "mix.o"] = (W, H * dv)
+        mlp = layer.get("mlp")
+        if mlp is None:
+            continue
+        out[p + "norm2"] = (W,)
+        out[p + "norm2b"] = (W,)
+        if mlp.get("kind", "dense") == "dense":
+            F = int(mlp["ff"])
+            out.update({p + "mlp.up": (F, W), p + "mlp.down": (W, F), p + "mlp.act": (4,)})
+        else:
+            E, F = int(mlp["router"]["experts"]), int(mlp["expert"]["ff"])
+            out.update({p + "mlp.router": (E, W), p + "mlp.router.b": (E,)})
+            for e in range(E):
+                out.update({p + f"mlp.e{e}.gate": (F, W), p + f"mlp.e{e}.up": (F, W), p + f"mlp.e{e}.down": (W, F)})
+    return out
+
+
+def random_weights(config: dict, seed: int, sharpen: float = 3.0) -> Dict[str, torch.Tensor]:
+    """Weights that make every mechanism matter: projections of unit gain, queries scaled by ``sharpen`` so that the
+    softmax is peaked, norm weights, shifts, averaging coefficients and router biases well away from 0 and 1."""
+    g = torch.Generator().manual_seed(seed)
+    out = {}
+    for name, shape in tensor_shapes(config).items():
+        last = name.rsplit(".", 1)[-1]
+        if len(shape) == 2:
+            t = torch.randn(shape, generator=g) / math.sqrt(shape[1])
+            if name.endswith("mix.q"):
+                t = t * sharpen
+            if name == "embed":
+                t = torch.randn(shape, generator=g)
+        elif last == "shift":
+            t = torch.rand(shape, generator=g) * 0.8 + 0.1
+        elif last == "dwa":
+            t = torch.softmax(torch.randn(shape, generator=g), 0) * 1.3
+        elif last == "act":
+            t = torch.tensor([0.8, 0.5, 0.3, 0.1]) + 0.2 * torch.randn(4, generator=g)
+        elif last == "b":
+            t = 0.5 * torch.randn(shape, generator=g)
+        elif last in ("lq1", "lk1", "lq2", "lk2"):
+            t = 0.4 * torch.randn(shape, generator=g)
+        elif name.endswith("dkv.norm"):
+            t = 1.0 + 0.2 * torch.randn(shape, generator=g)
+        else:                       # norms stored as their distance from one
+            t = 0.2 * torch.randn(shape, generator=g)
+        out[name] = t.to(torch.float32)
+    return out
+
+
+def forward(config: dict, weights: Dict[str, torch.Tensor], tokens, stored: Round = same, portions=None) -> torch.Tensor:
+    """Logits ``[T, vocab]`` of one sequence, fed whole or in the given portions."""
+    model = PlainVemepel(config, weights, stored)
+    state: dict = {}
+    if not portions:
+        return model.feed(state, list(tokens))
+    out, at = [], 0
+    for n in portions:
+        out.append(model.feed(state, list(tokens[at:at + n])))
+        at += n
+    assert at == len(tokens)
+    return torch.cat(out, 0)
