@@ -1,5 +1,6 @@
-"""``python bench.py --archs``: the Vabelorn and Lunadra architectures beside the Qwen3 dense decoder at equal layer sizes
-(``--arch-names`` picks among them; Lunadra's own kernels stand beside the like kernels of the Vabelorn path).
+"""``python bench.py --archs``: the Vabelorn, Lunadra and Vemepel architectures beside the Qwen3 dense decoder at equal layer
+sizes (``--arch-names`` picks among them; Lunadra's own kernels stand beside the like kernels of the Vabelorn path, Vemepel's
+beside those of the Qwen3 path).
 
 Random weights, bfloat16, one B200.  For each size: tokens/s of a 2,048-token prompt and of decode steps at batch 8
 (context 2,048) through ``ModelRunner.step``, for both architectures; then the kernels that only the new
@@ -412,6 +413,191 @@ def lunadra_kernel_pairs(pe, torch, s, hbm_gbs, prompt, batch, context):
     return out
 
 
+def vemepel_config(pe, s):
+    """Vemepel at the same width, heads and vocabulary: latent attention (a cached row of 512 + 64 features) and
+    differential attention (two maps of the head size over shared values, a chunk of 1,024 positions, the second such
+    layer reading the first one's keys), a PolyNorm feed-forward of two matrices as large as the gated one's three, and
+    routed experts whose two chosen ones together are as wide as the dense one."""
+    d = s["dim"]
+    lat = lambda kind: {"type": kind, "mixer": dict({"heads": s["heads"], "dim": d, "vdim": d, "kv_rank": 4 * d, "scale": (1.5 * d) ** -0.5},
+                                                   **({"rot_dim": d // 2, "rot": {"base": 1e6, "dims": d // 2}} if kind.endswith("_2") else {}))}
+    dif = lambda src: {"type": "attention", "mixer": dict({"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": d, "vdim": d,
+                                                           "scale": d ** -0.5, "diff": 0.5, "mask": {"size": 1024}},
+                                                          **({"kv_from": src} if src is not None else {}))}
+    dense = {"kind": "dense", "ff": s["ff"] * 3 // 2}
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": s["ff"] // 2}}
+    pattern = [dict(lat("latent_attention_2"), mlp=dense), dict(dif(None), mlp=moe), dict(lat("latent_attention"), mlp=dense),
+               dict(dif(1), mlp=moe)]
+    layers = []
+    for i in range(s["layers"]):
+        layer = dict(pattern[i % 4])
+        if "kv_from" in layer["mixer"]:
+            layer["mixer"] = dict(layer["mixer"], kv_from=i - 2)
+        layers.append(layer)
+    return pe.VemepelConfig.from_dict({"architecture": "Vemepel", "vocab": s["vocab"], "width": s["width"], "logit_scale": 1.0,
+                                       "norm": {"eps": 1e-6}, "layers": layers})
+
+
+def vemepel_kernel_pairs(pe, torch, s, peaks, prompt, batch, context):
+    """The kernels that only Vemepel has, each beside the like kernel of the Qwen3 path at the same shape.  A kernel's
+    roofline time is the larger of its bytes over the copy bandwidth and, for the attentions, its tensor-core operations
+    over the library product's rate; ``times_as_far_from_roofline`` divides the new kernel's distance from its roofline by
+    the like kernel's."""
+    ops = pe.kernels.ops
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    hbm_gbs, tflops = peaks["hbm_gbs"], peaks.get("bf16_tflops") or 1590.0
+    H, G, d, width, ff = s["heads"], s["kv_heads"], s["dim"], s["width"], s["ff"]
+    rank, dr = 4 * d, d // 2
+    row = rank + dr
+    flush = torch.zeros(96 * 2 ** 20, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = {}
+
+    held = {}
+
+    def buffer(name, shape, dtype):
+        key = (name, tuple(shape), dtype)
+        if key not in held:
+            held[key] = torch.empty(shape, dtype=dtype, device=dev)
+        return held[key]
+
+    def us_of(fn):
+        return 1e3 * timed(torch, fn, 20, 5, flush, graph=True)
+
+    def roof_us(nbytes, flops=0.0):
+        return max(nbytes / (hbm_gbs * 1e9), flops / (tflops * 1e12)) * 1e6
+
+    def entry(name, us_new, roof_new, like, us_like, roof_like):
+        out[name] = {"us": round(us_new, 2), "roofline_us": round(roof_new, 2), "of_roofline": round(roof_new / us_new, 3)}
+        if like:
+            out[name].update({"like_kernel": like, "like_us": round(us_like, 2), "like_of_roofline": round(roof_like / us_like, 3),
+                              "times_as_far_from_roofline": round((us_new / roof_new) / (us_like / roof_like), 2)})
+
+    for what, n_seqs, q_len, past in (("prompt", 1, prompt, 0), ("decode", batch, 1, context - 1)):
+        n = n_seqs * q_len
+        decode = q_len == 1
+        length = past + q_len
+        pages_per = -(-length // 64)
+        n_pages = n_seqs * pages_per
+        table = torch.arange(n_pages, dtype=torch.int32, device=dev).view(n_seqs, pages_per).contiguous()
+        qstart = torch.arange(0, n + 1, q_len, dtype=torch.int32, device=dev)
+        pasts = torch.full((n_seqs,), past, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        token_seq = torch.arange(n_seqs, dtype=torch.int32, device=dev).repeat_interleave(q_len).contiguous()
+        token_pos = (torch.arange(q_len, dtype=torch.int32, device=dev)[None] + past).repeat(n_seqs, 1).view(-1).contiguous()
+        where = (qstart, pasts, slots, table, n_pages)
+        pairs = n_seqs * (q_len * (q_len + 1) / 2 + q_len * past)        # (query, visible key) pairs without a chunk mask
+        # ---- the like kernels: the Qwen3 path's attention at its own shape
+        kp = torch.randn(n_pages, G, 64, d, device=dev).to(bf)
+        vp = torch.randn(n_pages, G, 64, d, device=dev).to(bf)
+        qkv = torch.randn(n, (H + 2 * G) * d, device=dev).to(bf)
+        o = torch.empty(n, H * d, dtype=bf, device=dev)
+        if decode:
+            sk, ms, fl = ops.attention_mma_decode_ranges(dev, d, n_seqs, G, context + 64, 512)
+            scratch = torch.empty(ops.attention_generic_scratch_floats(n_seqs, H, d, ms), device=dev)
+            like_att = "attention_mma (split + merge)"
+            us_att = us_of(lambda: ops.attention_mma(True, qkv, o, n_seqs, 1, H, G, d, 0.088, 0, *where, kp, vp, scratch, sk, ms, status,
+                                                     min_range_keys=fl))
+        else:
+            like_att = "attention_umma_prefill"
+            us_att = us_of(lambda: ops.attention_umma_prefill(qkv, o, n_seqs, q_len, H, G, d, 0.088, 0, *where, kp, vp, status))
+        roof_att = roof_us(n * H * d * 4 + n_seqs * length * 2 * G * d * 2, pairs * H * d * 4.0)
+        # ---- differential attention: 2H query maps over 2G key heads and G value heads, a chunk of 1,024 positions
+        chunk = 1024
+        kp2 = torch.randn(n_pages, 2 * G, 64, d, device=dev).to(bf)
+        q2 = torch.randn(n, 2 * H * d, device=dev).to(bf)
+        maps = torch.empty(n, 2 * H * d, device=dev)
+        new = pe.parts.diff_attention.attend_maps
+        seen = min(length, chunk) if decode else None
+        dpairs = n_seqs * seen if decode else sum(min(chunk, q_len - c) * (min(chunk, q_len - c) + 1) / 2 for c in range(0, q_len, chunk))
+        keys_read = n_seqs * (seen if decode else length)
+        us = us_of(lambda: new(ops, decode, q2, maps, n_seqs, q_len, H, G, d, d, d ** -0.5, chunk, *where, kp2, vp, status,
+                               context + 64, buffer))
+        entry(f"{what}: differential attention, two maps, chunk mask", us,
+              roof_us(n * 2 * H * d * (2 + 4) + keys_read * 3 * G * d * 2, dpairs * 2 * H * d * 4.0), like_att, us_att, roof_att)
+        heads_o = torch.empty(n, H * d, dtype=bf, device=dev)
+        us = us_of(lambda: ops.diff_combine(maps, heads_o, H, d, 0.4, 1e-6, 0.5))
+        w = torch.ones(H * d, device=dev)
+        xin = torch.randn(n, H * d, device=dev).to(bf)
+        us_like = us_of(lambda: ops.rmsnorm(xin, w, heads_o, 1e-6))
+        entry(f"{what}: difference of the maps, head norm", us, roof_us(n * H * d * (8 + 2)), "rmsnorm", us_like, roof_us(n * H * d * 4))
+        # ---- latent attention: H query heads of rank + dr features over one cached row a position
+        lp = torch.randn(n_pages, 1, 64, row, device=dev).to(bf)
+        qf = (torch.randn(n, H * row, device=dev) * 0.3).to(bf)
+        mixed = torch.empty(n, H * rank, dtype=bf, device=dev)
+        lat = pe.parts.latent_attention.attend_rows
+        us = us_of(lambda: lat(ops, decode, qf, mixed, n_seqs, q_len, H, row, rank, 0.07, *where, lp, status, context + 64, buffer))
+        entry(f"{what}: latent attention over the cached rows ({rank} + {dr} features)", us,
+              roof_us(n * H * (row + rank) * 2 + n_seqs * length * row * 2, pairs * H * (row + rank) * 2.0), like_att, us_att, roof_att)
+        # ---- the latent rows' norm, rotation and append beside q/k-norm, rotation and append
+        rope = pe.parts.lookup("position", "rope")
+        rt = pe.parts.Runtime(dev, bf)
+        pos_i = rope({"rotary_dim": dr, "theta": 1e6, "max_positions": context + 64, "style": "interleaved", "exact": True}, {}, rt)
+        pos_q = rope({"rotary_dim": d, "theta": 1e6, "max_positions": context + 64}, {}, rt)
+        ci, si, ri = pos_i.tables()
+        cq, sq, _ = pos_q.tables()
+        cols = H * (d + dr) + row + H
+        qlg = torch.randn(n, cols, device=dev).to(bf)
+        absorbed = torch.randn(H, n, rank, device=dev).to(bf)
+        qfull = torch.empty(n, H, row, dtype=bf, device=dev)
+        nw = torch.ones(rank, device=dev)
+        us = us_of(lambda: ops.latent_prepare(qlg, 0, H * (d + dr), H, d, dr, rank, nw, 1e-6, ci, si, ri, token_seq, token_pos, slots,
+                                              table, n_pages, lp, qfull, True, status, absorbed=absorbed))
+        qw, kw = torch.ones(d, device=dev), torch.ones(d, device=dev)
+        us_like = us_of(lambda: ops.qk_norm_rope_append(qkv, n, H, G, d, qw, kw, 1e-6, cq, sq, d, token_seq, token_pos, slots, qstart, table,
+                                                        n_pages, kp, vp, True, status))
+        entry(f"{what}: latent row's norm, rotation, append, queries put together", us,
+              roof_us(n * (H * dr + row) * 2 + n * H * rank * 2 + n * H * row * 2 + n * row * 2), "qk_norm_rope_append", us_like,
+              roof_us(n * (H + 2 * G) * d * 2 + n * (H + G) * d * 2 + n * 2 * G * d * 2))
+        kv_rows = torch.randn(n, 3 * G * d, device=dev).to(bf)
+
+        def append():
+            ops.rows_to_pages(kv_rows, 0, 2 * G, d, token_seq, token_pos, slots, table, n_pages, kp2, status)
+            ops.rows_to_pages(kv_rows, 2 * G * d, G, d, token_seq, token_pos, slots, table, n_pages, vp, status)
+        entry(f"{what}: two key maps and the values into their pages (2 kernels)", us_of(append), roof_us(n * 3 * G * d * 4),
+              "qk_norm_rope_append", us_like, roof_us(n * (H + 2 * G) * d * 2 + n * (H + G) * d * 2 + n * 2 * G * d * 2))
+        # ---- gates, norms and the stream
+        heads_t = torch.randn(H, n, d, device=dev).to(bf)
+        gate = torch.randn(n, H * d, device=dev).to(bf)
+        us = us_of(lambda: ops.sigmoid_gate(heads_t, gate, heads_o))
+        gu = torch.randn(n, 2 * ff, device=dev).to(bf)
+        act = torch.empty(n, ff, dtype=bf, device=dev)
+        us_silu = us_of(lambda: ops.silu_mul(gu, act))
+        entry(f"{what}: sigmoid gate a feature on the heads' outputs", us, roof_us(n * H * d * 6), "silu_mul", us_silu, roof_us(n * ff * 6))
+        z = torch.randn(n, ff * 3 // 2, device=dev).to(bf)
+        pz = torch.empty_like(z)
+        coeff = torch.tensor([0.5, 0.3, 0.2, 0.1], device=dev)
+        us = us_of(lambda: ops.polynorm(z, coeff, 1e-6, pz))
+        entry(f"{what}: PolyNorm activation", us, roof_us(n * (ff * 3 // 2) * 4), "silu_mul", us_silu, roof_us(n * ff * 6))
+        stream = torch.randn(n, width, device=dev)
+        delta = torch.randn(n, width, device=dev).to(bf)
+        wn = torch.ones(width, device=dev)
+        normed = torch.empty(n, width, dtype=bf, device=dev)
+        mix = torch.rand(width, device=dev)
+        prev = torch.zeros(n_seqs, width, device=dev)
+        us = us_of(lambda: ops.norm_token_shift(stream, wn, 1e-6, mix, prev, token_seq, slots, qstart, normed, status))
+        us_like = us_of(lambda: ops.rmsnorm_residual(stream, delta, wn, normed, 1e-6))
+        entry(f"{what}: norm and token shift", us, roof_us(n * width * (4 + 2)), "rmsnorm_residual", us_like, roof_us(n * width * (8 + 2 + 2)))
+        depth = s["layers"]
+        results = torch.randn(depth + 1, n, width, device=dev)
+        co = torch.rand(depth + 1, device=dev)
+        avg = torch.empty(n, width, device=dev)
+        us = us_of(lambda: ops.depth_average(results, co, depth + 1, avg, None))
+        entry(f"{what}: average over {depth + 1} results of the depth", us, roof_us(n * width * 4 * (depth + 2)), "rmsnorm_residual", us_like,
+              roof_us(n * width * (8 + 2 + 2)))
+        # ---- the router by logits beside the router by probabilities
+        E, top = 8, 2
+        logits = torch.randn(n, E, device=dev)
+        bias = torch.zeros(E, device=dev)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(n, top, device=dev)
+        us = us_of(lambda: ops.moe_route_logits(logits, bias, top, chosen, weight))
+        us_like = us_of(lambda: ops.moe_route(logits, bias, top, chosen, weight))
+        entry(f"{what}: experts chosen by their logits", us, roof_us(n * (E * 4 + top * 8)), "moe_route", us_like, roof_us(n * (E * 4 + top * 8)))
+    return out
+
+
 def main(args):
     import torch
 
@@ -428,8 +614,9 @@ def main(args):
     for name in names:
         s = SIZES[name]
         row = {"shape": s}
-        wanted = [a for a in (args.arch_names or "vabelorn,qwen3,lunadra").split(",") if a]
-        for arch, make in (("vabelorn", vabelorn_config), ("qwen3", qwen3_config), ("lunadra", lunadra_config)):
+        wanted = [a for a in (args.arch_names or "vabelorn,qwen3,lunadra,vemepel").split(",") if a]
+        for arch, make in (("vabelorn", vabelorn_config), ("qwen3", qwen3_config), ("lunadra", lunadra_config),
+                           ("vemepel", vemepel_config)):
             if arch not in wanted:
                 continue
             row[arch] = model_speeds(pe, torch, make(pe, s), prompt, batch, context, args.steps, max(args.warmup, 3))
@@ -441,6 +628,10 @@ def main(args):
         if "lunadra" in wanted:
             row["lunadra_kernels"] = lunadra_kernel_pairs(pe, torch, s, peaks["hbm_gbs"], prompt, batch, context)
             for k, v in row["lunadra_kernels"].items():
+                print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
+        if "vemepel" in wanted:
+            row["vemepel_kernels"] = vemepel_kernel_pairs(pe, torch, s, peaks, prompt, batch, context)
+            for k, v in row["vemepel_kernels"].items():
                 print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
         result["sizes"][name] = row
     result["gpu_launches"] = pe.kernels.ops.launch_count()

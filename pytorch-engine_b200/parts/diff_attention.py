@@ -36,6 +36,20 @@ def maps_first(w: torch.Tensor, heads: int, d: int) -> torch.Tensor:
     return w.view(heads, 2, d, w.shape[1]).transpose(0, 1).reshape(2 * heads * d, w.shape[1]).contiguous()
 
 
+def attend_maps(ops, decode, q, maps, n_seqs, max_q, n_heads, n_kv_heads, d, dv, scale, chunk, seq_qstart, seq_past, seq_slot,
+                page_table, num_pages, k_pages, v_pages, status, max_kv_len, buffer) -> None:
+    """Both softmax maps of every head as one grouped-query attention: ``q [n, 2 * n_heads * d]`` ([map][head][d]) over
+    ``k_pages [pages, 2 * n_kv_heads, 64, d]`` and ``v_pages [pages, n_kv_heads, 64, dv]`` into ``maps [n, 2 * n_heads * dv]``
+    float32.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step."""
+    scratch, max_splits = None, 0
+    if decode:
+        max_splits = max(1, -(-int(max_kv_len) // SPLIT_KEYS))
+        scratch = buffer("attn.scratch", (ops.attention_generic_scratch_floats(n_seqs, 2 * n_heads, dv, max_splits),), torch.float32)
+    ops.attention_generic_masked(decode, q, maps, n_seqs, max_q, 2 * n_heads, 2 * n_kv_heads, d, dv, scale, seq_qstart, seq_past,
+                                 seq_slot, page_table, num_pages, k_pages, v_pages, scratch, SPLIT_KEYS, max_splits, status,
+                                 chunk=chunk, v_heads=n_kv_heads)
+
+
 @register("mixer", "diff_attention")
 class DiffAttention:
     """params: ``hidden``, ``n_heads``, ``n_kv_heads``, ``head_dim``, ``v_head_dim``, ``scale``, ``diff``, ``eps``, ``chunk``
@@ -102,14 +116,9 @@ class DiffAttention:
             ops.rows_to_pages(qkv, self.q_cols, 2 * nkv, d, *where, view.k_pages, rt.status)
             ops.rows_to_pages(qkv, self.q_cols + self.k_cols, nkv, dv, *where, view.v_pages, rt.status)
         maps = ctx.buffer("diff.maps", (n, 2 * nh * dv), torch.float32)   # the two maps stay float32 up to their difference
-        scratch, max_splits = None, 0
-        if ctx.decode:
-            max_splits = ctx.max_splits(SPLIT_KEYS)
-            scratch = ctx.buffer("attn.scratch", (ops.attention_generic_scratch_floats(ctx.n_seqs, 2 * nh, dv, max_splits),),
-                                 torch.float32)
-        ops.attention_generic_masked(ctx.decode, qkv, maps, ctx.n_seqs, ctx.max_q, 2 * nh, 2 * nkv, d, dv, self.scale,
-                                     ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
-                                     view.v_pages, scratch, SPLIT_KEYS, max_splits, rt.status, chunk=self.chunk, v_heads=nkv)
+        attend_maps(ops, ctx.decode, qkv, maps, ctx.n_seqs, ctx.max_q, nh, nkv, d, dv, self.scale, self.chunk, ctx.seq_qstart,
+                    ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages, view.v_pages, rt.status,
+                    ctx.max_kv_len, ctx.buffer)
         heads = ctx.buffer("diff.heads", (n, nh * dv), rt.dtype)
         ops.diff_combine(maps, heads, nh, dv, self.lam, self.eps, 1.0 - self.diff)
         delta = ctx.buffer("diff.delta", (n, self.hidden), rt.dtype)

@@ -29,6 +29,19 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
+def attend_rows(ops, decode, qfull, mixed, n_seqs, max_q, n_heads, row, rank, scale, seq_qstart, seq_past, seq_slot, page_table,
+                num_pages, pages, status, max_kv_len, buffer) -> None:
+    """Every head's query of ``row`` features (``qfull [n, n_heads * row]``) over the cached rows ``pages [pages, 1, 64, row]``
+    as one kv head whose values are the rows' leading ``rank`` features; ``mixed [n, n_heads * rank]`` gets the weighted
+    rows.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step."""
+    scratch, max_splits = None, 0
+    if decode:
+        max_splits = max(1, -(-int(max_kv_len) // SPLIT_KEYS))
+        scratch = buffer("attn.scratch", (ops.attention_generic_scratch_floats(n_seqs, n_heads, rank, max_splits),), torch.float32)
+    ops.attention_generic_masked(decode, qfull, mixed, n_seqs, max_q, n_heads, 1, row, rank, scale, seq_qstart, seq_past, seq_slot,
+                                 page_table, num_pages, pages, pages, scratch, SPLIT_KEYS, max_splits, status, v_ld=row)
+
+
 @register("mixer", "latent_attention")
 class LatentAttention:
     """params: ``hidden``, ``n_heads``, ``head_dim`` (features without position), ``rot_dim`` (rotated features, 0: none),
@@ -119,14 +132,9 @@ class LatentAttention:
                            ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages, pages, qfull, writes_cache, rt.status,
                            absorbed=absorbed)
         mixed = ctx.buffer("latent.mixed", (n, nh, r), rt.dtype)
-        scratch, max_splits = None, 0
-        if ctx.decode:
-            max_splits = ctx.max_splits(SPLIT_KEYS)
-            scratch = ctx.buffer("attn.scratch", (ops.attention_generic_scratch_floats(ctx.n_seqs, nh, r, max_splits),),
-                                 torch.float32)
-        ops.attention_generic_masked(ctx.decode, qfull.view(n, nh * row), mixed.view(n, nh * r), ctx.n_seqs, ctx.max_q, nh, 1,
-                                     row, r, self.scale, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table,
-                                     view.num_pages, pages, pages, scratch, SPLIT_KEYS, max_splits, rt.status, v_ld=row)
+        attend_rows(ops, ctx.decode, qfull.view(n, nh * row), mixed.view(n, nh * r), ctx.n_seqs, ctx.max_q, nh, row, r, self.scale,
+                    ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, pages, rt.status, ctx.max_kv_len,
+                    ctx.buffer)
         # expand with W_uv head by head: [heads, n, rank] x [heads, rank, dv]
         heads_t = ctx.buffer("latent.heads_t", (nh, n, dv), rt.dtype)
         rt.batched_linear(mixed.transpose(0, 1), self.uv_t.transpose(1, 2), heads_t)
