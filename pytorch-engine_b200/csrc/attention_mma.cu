@@ -48,7 +48,29 @@ struct Args {
   // query's position (interleaved pairs over the whole head; tables [out_rows, HD/2]); off: 0 and null
   int sink;
   const float* out_cos; const float* out_sin; int out_rows;
+  // chunk > 0: a key is visible only inside the query's own block of `chunk` positions (counted from position 0);
+  // v_heads: value heads in a page, kv head g reads value head g % v_heads (several key maps over one set of values);
+  // out_f32 != 0: `out` is float32 and out_ld counts floats (not with a turned output)
+  int chunk, v_heads, out_f32;
+  // split_p != 0: a probability enters the P.V product as two bfloat16 terms (its rounding, and the rounding of what
+  // that left over), in two products: 16 significant bits of every weight instead of 8
+  int split_p;
 };
+
+// What rounding (p0, p1) to bfloat16 left over, as a bfloat16 pair.
+__device__ __forceinline__ uint32_t pack_bf16_rest(float p0, float p1) {
+  const __nv_bfloat162 lead = __floats2bfloat162_rn(p0, p1);
+  const __nv_bfloat162 rest = __floats2bfloat162_rn(p0 - __bfloat162float(lead.x), p1 - __bfloat162float(lead.y));
+  return *reinterpret_cast<const uint32_t*>(&rest);
+}
+
+// First visible key of a query at `qpos` under the window and chunk masks.
+__device__ __forceinline__ int first_visible(const Args& a, int qpos) {
+  int lo = 0;
+  if (a.window > 0) lo = max(lo, qpos - a.window + 1);
+  if (a.chunk > 0) lo = max(lo, qpos / a.chunk * a.chunk);
+  return lo;
+}
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -96,11 +118,12 @@ __device__ __forceinline__ void issue_page(const Args& a, const CUtensorMap* kma
     page = 0;
   }
   const int y = (page * a.n_kv_heads + kvh) * BN;
+  const int yv = (page * a.v_heads + kvh % a.v_heads) * BN;
   tma::mbar_expect_tx(bar, 2 * BN * HD * 2);
 #pragma unroll
   for (int sub = 0; sub < HD / 64; ++sub) {
     tma::load_2d(stage + sub * (BN * 128), kmap, sub * 64, y, bar);
-    tma::load_2d(stage + BN * HD * 2 + sub * (BN * 128), vmap, sub * 64, y, bar);
+    tma::load_2d(stage + BN * HD * 2 + sub * (BN * 128), vmap, sub * 64, yv, bar);
   }
 }
 
@@ -118,8 +141,8 @@ __device__ __forceinline__ char* align_1024(char* p) {
 
 // ---- prefill ---------------------------------------------------------------------------------------
 // grid: (row tiles of 64, n_kv_heads, n_seqs); block: 128 threads.
-template <int HD>
-__global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
+template <int HD, bool SPLIT_P>
+__global__ void __launch_bounds__(128, SPLIT_P ? 2 : 3) prefill_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
                                                       const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
   __shared__ uint64_t bars[2];
@@ -143,8 +166,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
   const int slot = a.seq_slot[b];
   const int last_row = min(n_rows, row0 + 64) - 1;
   const int first_pos = past + row0 / group, last_pos = past + last_row / group;
-  int k_begin = 0;
-  if (a.window > 0) k_begin = max(0, first_pos - a.window + 1) / BN * BN;
+  const int k_begin = first_visible(a, first_pos) / BN * BN;
   const int k_end = last_pos + 1;
   const int n_tiles = (k_end - k_begin + BN - 1) / BN;
 
@@ -179,6 +201,8 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
   const int pos_lo = past + r_lo / group, pos_hi = past + r_hi / group;   // rows beyond n_rows are never stored
   const int warp_last_pos = past + min(n_rows - 1, row0 + warp * 16 + 15) / group;
   const int warp_first_pos = past + min(n_rows - 1, row0 + warp * 16) / group;
+  const int warp_first_lo = first_visible(a, warp_first_pos), warp_last_lo = first_visible(a, warp_last_pos);
+  const int lo_lo = first_visible(a, pos_lo), lo_hi = first_visible(a, pos_hi);
   float o[NO][4];
 #pragma unroll
   for (int n = 0; n < NO; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
@@ -194,7 +218,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       give_up(a, bars, 2, 1);
       return;
     }
-    const bool skip = (k0 > warp_last_pos) || (a.window > 0 && k0 + BN - 1 <= warp_first_pos - a.window);
+    const bool skip = (k0 > warp_last_pos) || (k0 + BN - 1 < warp_first_lo);
     if (!skip) {
       const uint32_t ks_base = smem_u32(stage), vs_base = ks_base + BN * HD * 2;
       float s[8][4];
@@ -214,7 +238,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       // scale, mask, running max
       float mx_lo = -INFINITY, mx_hi = -INFINITY;
       // a page that lies wholly in the past of every row of this warp (and inside every window) needs no mask
-      const bool full = (k0 + BN - 1 <= warp_first_pos) && (a.window <= 0 || k0 > warp_last_pos - a.window);
+      const bool full = (k0 + BN - 1 <= warp_first_pos) && (k0 >= warp_last_lo);
       if (full) {
 #pragma unroll
         for (int n = 0; n < 8; ++n) {
@@ -232,8 +256,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
           for (int e = 0; e < 4; ++e) {
             const int kpos = k0 + n * 8 + 2 * t + (e & 1);
             const int qpos = (e < 2) ? pos_lo : pos_hi;
-            bool vis = kpos <= qpos;
-            if (a.window > 0) vis = vis && (kpos > qpos - a.window);
+            const bool vis = kpos <= qpos && kpos >= ((e < 2) ? lo_lo : lo_hi);
             const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
             s[n][e] = v;
             if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -250,6 +273,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       const float base_lo = (mn_lo == -INFINITY) ? 0.f : mn_lo, base_hi = (mn_hi == -INFINITY) ? 0.f : mn_hi;
       float sum_lo = 0.f, sum_hi = 0.f;
       uint32_t pf[4][4];  // P as A operand: 4 k-steps of 16 keys
+      uint32_t pr[SPLIT_P ? 4 : 1][4];  // what its rounding left over
 #pragma unroll
       for (int n = 0; n < 8; ++n) {
         const float p0 = fast_exp2(s[n][0] - base_lo), p1 = fast_exp2(s[n][1] - base_lo);
@@ -258,6 +282,10 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
         sum_hi += p2 + p3;
         pf[n >> 1][(n & 1) * 2] = pack_bf16(p0, p1);
         pf[n >> 1][(n & 1) * 2 + 1] = pack_bf16(p2, p3);
+        if (SPLIT_P) {
+          pr[n >> 1][(n & 1) * 2] = pack_bf16_rest(p0, p1);
+          pr[n >> 1][(n & 1) * 2 + 1] = pack_bf16_rest(p2, p3);
+        }
       }
       sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 1);
       sum_lo += __shfl_xor_sync(0xffffffffu, sum_lo, 2);
@@ -280,6 +308,10 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
           ldmatrix_x4_trans(vb, vs_base + tile_off<HD>(key, np * 2 + (lane >> 4)));
           mma_bf16(o[np * 2], pf[kk], vb[0], vb[1]);
           mma_bf16(o[np * 2 + 1], pf[kk], vb[2], vb[3]);
+          if (SPLIT_P) {
+            mma_bf16(o[np * 2], pr[kk], vb[0], vb[1]);
+            mma_bf16(o[np * 2 + 1], pr[kk], vb[2], vb[3]);
+          }
         }
       }
     }
@@ -314,6 +346,13 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
       }
       continue;
     }
+    if (a.out_f32) {
+      float* dstf = reinterpret_cast<float*>(a.out) + (size_t)(q0 + tok) * a.out_ld + (size_t)head * HD;
+#pragma unroll
+      for (int n = 0; n < NO; ++n)
+        *reinterpret_cast<float2*>(dstf + n * 8 + 2 * t) = make_float2(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
+      continue;
+    }
 #pragma unroll
     for (int n = 0; n < NO; ++n) {
       const uint32_t v = pack_bf16(o[n][half * 2] * inv, o[n][half * 2 + 1] * inv);
@@ -324,7 +363,7 @@ __global__ void __launch_bounds__(128, 3) prefill_kernel(Args a, const __grid_co
 
 // One warp folds its 16 keys (key0 .. key0+15 of the page that starts at position k0) into the
 // running softmax state of the group's rows.  Keys outside [k_first, k_hi) are masked.
-template <int HD>
+template <int HD, bool SPLIT_P>
 __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_base, int key0, int k0, int k_first,
                                                  int k_hi, float scale_log2, const uint32_t (&qf)[HD / 16][4],
                                                  float (&o)[HD / 8][4], float& m_lo, float& m_hi, float& l_lo,
@@ -378,6 +417,11 @@ __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_b
   m_hi = mn_hi;
   uint32_t pf[4];
   pf[0] = pack_bf16(p00, p01); pf[1] = pack_bf16(p02, p03); pf[2] = pack_bf16(p10, p11); pf[3] = pack_bf16(p12, p13);
+  uint32_t pr[4] = {0u, 0u, 0u, 0u};
+  if (SPLIT_P) {
+    pr[0] = pack_bf16_rest(p00, p01); pr[1] = pack_bf16_rest(p02, p03);
+    pr[2] = pack_bf16_rest(p10, p11); pr[3] = pack_bf16_rest(p12, p13);
+  }
 #pragma unroll
   for (int n = 0; n < NO; ++n) {
     o[n][0] *= al_lo; o[n][1] *= al_lo; o[n][2] *= al_hi; o[n][3] *= al_hi;
@@ -389,6 +433,10 @@ __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_b
     ldmatrix_x4_trans(vb, vs_base + tile_off<HD>(key, np * 2 + (lane >> 4)));
     mma_bf16(o[np * 2], pf, vb[0], vb[1]);
     mma_bf16(o[np * 2 + 1], pf, vb[2], vb[3]);
+    if (SPLIT_P) {
+      mma_bf16(o[np * 2], pr, vb[0], vb[1]);
+      mma_bf16(o[np * 2 + 1], pr, vb[2], vb[3]);
+    }
   }
 }
 }
@@ -406,7 +454,7 @@ __device__ __forceinline__ int range_keys(const Args& a, int len) {
 }
 
 // grid: (max_splits, n_kv_heads, n_seqs); block: 128 threads; STAGES pages in flight.
-template <int HD, int STAGES>
+template <int HD, int STAGES, bool SPLIT_P>
 __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_constant__ CUtensorMap kmap,
                                                            const __grid_constant__ CUtensorMap vmap) {
   extern __shared__ char smem_raw[];
@@ -428,7 +476,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
   const int per_range = range_keys(a, len);
   const int k_lo = split * per_range, k_hi = min(len, k_lo + per_range);
   if (k_lo >= len) return;
-  const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
+  const int win_lo = first_visible(a, len - 1);
   if (k_hi <= win_lo) return;
   const int slot = a.seq_slot[b];
   const int k_first = max(k_lo, win_lo);         // first visible key of this range
@@ -480,7 +528,7 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
       return;
     }
     const int k0 = k_begin + it * BN;
-    decode_fold_page<HD>(smem_u32(smem + (it % STAGES) * STAGE), smem_u32(smem + (it % STAGES) * STAGE) + BN * HD * 2,
+    decode_fold_page<HD, SPLIT_P>(smem_u32(smem + (it % STAGES) * STAGE), smem_u32(smem + (it % STAGES) * STAGE) + BN * HD * 2,
                          warp * 16, k0, k_first, k_hi, a.scale_log2, qf, o, m_lo, m_hi, l_lo, l_hi, lane);
     __syncthreads();
   }
@@ -538,7 +586,7 @@ __global__ void decode_merge_kernel(Args a) {
     if (threadIdx.x == 0) report(a.status, kStatusPositionOutOfRange, b, len - 1, per_range * a.max_splits);
     n_splits = a.max_splits;
   }
-  const int win_lo = a.window > 0 ? max(0, len - a.window) : 0;
+  const int win_lo = first_visible(a, len - 1);
   const int first = min(win_lo / per_range, n_splits);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   __nv_bfloat16* o = a.out + (size_t)tq * a.out_ld + (size_t)h * HD;
@@ -584,7 +632,8 @@ __global__ void decode_merge_kernel(Args a) {
       const float cs = a.out_cos[(size_t)pos * (HD / 2) + (c >> 1)], sn = a.out_sin[(size_t)pos * (HD / 2) + (c >> 1)];
       v = (c & 1) ? v * cs - other * sn : v * cs + other * sn;
     }
-    o[c] = __float2bfloat16_rn(v);
+    if (a.out_f32) reinterpret_cast<float*>(a.out)[(size_t)tq * a.out_ld + (size_t)h * HD + c] = v;
+    else o[c] = __float2bfloat16_rn(v);
   }
 }
 
@@ -598,17 +647,17 @@ static int opt_in(K kernel, size_t bytes) {
   return 0;
 }
 
-template <int HD>
+template <int HD, bool SPLIT_P>
 static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_t stream) {
   constexpr int STAGE = 2 * BN * HD * 2;
   CUtensorMap kmap, vmap;
   const uint64_t rows = (uint64_t)a.num_pages * a.n_kv_heads * BN;
   int me = tma::make_map_2d_bf16(&kmap, a.k_pages, HD, rows, HD, 64, BN);
-  if (me == 0) me = tma::make_map_2d_bf16(&vmap, a.v_pages, HD, rows, HD, 64, BN);
+  if (me == 0) me = tma::make_map_2d_bf16(&vmap, a.v_pages, HD, (uint64_t)a.num_pages * a.v_heads * BN, HD, 64, BN);
   if (me != 0) return me < 0 ? me : PE_ERR_BAD_ARGUMENT;
   if (!decode) {
     const size_t smem = 1024 + 2 * STAGE;
-    auto k = prefill_kernel<HD>;
+    auto k = prefill_kernel<HD, SPLIT_P>;
     int e = opt_in(k, smem);
     if (e) return e;
     const long long tiles = ((long long)max_q * a.group + 63) / 64;
@@ -631,7 +680,7 @@ static int launch(const Args& a, bool decode, int n_seqs, int max_q, cudaStream_
     return 0;
   };
   // three stages: two blocks per SM, two pages in flight per block (measured best of 2, 3, 4)
-  const int e = go(decode_split_kernel<HD, 3>, 3);
+  const int e = go(decode_split_kernel<HD, 3, SPLIT_P>, 3);
   if (e) return e;
   PE_LAUNCH_CHECK();
   // The merge starts when the split kernel has completed, not while it drains: with the early start a
@@ -684,11 +733,30 @@ extern "C" int pe_attention_mma_ex(int decode, const void* q, long long q_ld, vo
                                    const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
                                    int num_pages, const void* k_pages, const void* v_pages, float* scratch,
                                    int split_keys, int max_splits, int min_range_keys, int* status, cudaStream_t stream) {
+  return pe_attention_mma_masked(decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim, scale, window,
+                                 0, n_kv_heads, 0, 0, sink, out_cos, out_sin, out_rows, seq_qstart, seq_past, seq_slot,
+                                 page_table, table_stride, num_pages, k_pages, v_pages, scratch, split_keys, max_splits,
+                                 min_range_keys, status, stream);
+}
+
+// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), `v_heads` value
+// heads a page (kv head g reads value head g % v_heads), optionally a float32 output (`out_f32`: out_ld counts floats)
+// and optionally (`split_p`) every probability as two bfloat16 terms in the P.V product.
+extern "C" int pe_attention_mma_masked(int decode, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs,
+                                       int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
+                                       int chunk, int v_heads, int out_f32, int split_p, int sink, const float* out_cos,
+                                       const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past,
+                                       const int* seq_slot, const int* page_table, int table_stride, int num_pages,
+                                       const void* k_pages, const void* v_pages, float* scratch, int split_keys,
+                                       int max_splits, int min_range_keys, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if ((out_cos == nullptr) != (out_sin == nullptr)) return PE_ERR_BAD_ARGUMENT;
+  if (chunk < 0 || v_heads <= 0 || (out_f32 && out_cos)) return PE_ERR_BAD_ARGUMENT;
   if (!pe_attention_mma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
-  // 16-byte vector loads of q rows
-  if ((q_ld * 2) % 16 || ((uintptr_t)q % 16) || (out_ld * 2) % 4 || ((uintptr_t)out % 4)) return PE_ERR_BAD_ARGUMENT;
+  // 16-byte vector loads of q rows; 4-byte (bfloat16 pairs) or 8-byte (float pairs) stores of output rows
+  const int out_bytes = out_f32 ? 4 : 2;
+  if ((q_ld * 2) % 16 || ((uintptr_t)q % 16) || (out_ld * out_bytes) % (2 * out_bytes) || ((uintptr_t)out % (2 * out_bytes)))
+    return PE_ERR_BAD_ARGUMENT;
   if (((uintptr_t)k_pages % 16) || ((uintptr_t)v_pages % 16)) return PE_ERR_BAD_ARGUMENT;
   pe::fa::Args a;
   a.q = (const __nv_bfloat16*)q; a.q_ld = q_ld; a.out = (__nv_bfloat16*)out; a.out_ld = out_ld;
@@ -699,6 +767,7 @@ extern "C" int pe_attention_mma_ex(int decode, const void* q, long long q_ld, vo
   a.k_pages = (const __nv_bfloat16*)k_pages; a.v_pages = (const __nv_bfloat16*)v_pages; a.status = status;
   a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0; a.min_range_keys = 0;
   a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin; a.out_rows = out_rows;
+  a.chunk = chunk; a.v_heads = v_heads; a.out_f32 = out_f32; a.split_p = split_p;
   if (decode) {
     if (!scratch || split_keys < 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
     if (min_range_keys < 0 || min_range_keys % pe::fa::BN) return PE_ERR_BAD_ARGUMENT;
@@ -706,6 +775,10 @@ extern "C" int pe_attention_mma_ex(int decode, const void* q, long long q_ld, vo
     a.part_acc = scratch;
     a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;
   }
-  if (head_dim == 64) return pe::fa::launch<64>(a, decode != 0, n_seqs, max_q, stream);
-  return pe::fa::launch<128>(a, decode != 0, n_seqs, max_q, stream);
+  if (split_p) {
+    if (head_dim == 64) return pe::fa::launch<64, true>(a, decode != 0, n_seqs, max_q, stream);
+    return pe::fa::launch<128, true>(a, decode != 0, n_seqs, max_q, stream);
+  }
+  if (head_dim == 64) return pe::fa::launch<64, false>(a, decode != 0, n_seqs, max_q, stream);
+  return pe::fa::launch<128, false>(a, decode != 0, n_seqs, max_q, stream);
 }

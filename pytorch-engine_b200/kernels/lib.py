@@ -72,6 +72,10 @@ _SIGNATURES = {
     "pe_attention_generic_ex": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, P, P, I, I, I, P, P, P, P, I, I, P, P, P,
                                 I, I, P, P],
     "pe_attention_mma_ex": [I, P, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
+    "pe_attention_mma_masked": [I, P, L, P, L, I, I, I, I, I, F, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I,
+                                P, P],
+    "pe_attention_latent_supported": [I, I],
+    "pe_attention_latent": [I, P, L, P, L, I, I, I, I, I, F, P, P, P, P, I, I, P, P, I, I, I, P, P],
     "pe_attention_umma_prefill_ex": [P, L, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, I, P, P, P],
     "pe_attention_decode_noalloc": [I, P, L, P, L, I, I, I, I, F, I, P, P, P, P, I, I, P, P, I, I, P, P],
     "pe_embed_pair_gather": [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],

@@ -311,6 +311,57 @@ def attention_mma(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int,
     _count(2 if decode else 1)
 
 
+def attention_mma_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int,
+                         n_kv_heads: int, head_dim: int, scale: float, seq_qstart: torch.Tensor, seq_past: torch.Tensor,
+                         seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
+                         v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int, max_splits: int,
+                         status: torch.Tensor, min_range_keys: int = 0, window: int = 0, chunk: int = 0,
+                         v_heads: Optional[int] = None, split_p: bool = False) -> None:
+    """``attention_mma`` with a chunk mask (``chunk`` > 0: a query sees the keys of its own block of that many positions,
+    blocks counted from position 0), ``v_heads`` value heads in ``v_pages`` (kv head g reads value head g % v_heads: several
+    key maps over one set of values), an output of bfloat16 or float32 (by ``out``'s dtype) and, with ``split_p``, every
+    softmax weight as two bfloat16 terms in the product with the values (16 significant bits instead of 8)."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
+    _need(q.dtype == k_pages.dtype == v_pages.dtype == torch.bfloat16, "attention_mma: bfloat16 inputs only")
+    _need(out.dtype in (torch.bfloat16, torch.float32), "attention_mma: out bfloat16 or float32")
+    check(library().pe_attention_mma_masked(
+        1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads, head_dim,
+        float(scale), int(window), int(chunk), int(n_kv_heads if v_heads is None else v_heads),
+        1 if out.dtype == torch.float32 else 0, 1 if split_p else 0, 0, None, None, 0, _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot),
+        _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
+        int(min_range_keys), _ptr(status), _stream()), "attention_mma_masked")
+    _count(2 if decode else 1)
+
+
+def attention_latent_supported(dtype: torch.dtype, row: int, rank: int) -> bool:
+    """Whether the tensor-core kernels of csrc/attention_latent.cu take cached rows of ``row`` features whose leading
+    ``rank`` are the values (bfloat16; rows in steps of 64 up to 576; values of 128, 256 or 512 features)."""
+    return dtype == torch.bfloat16 and bool(library().pe_attention_latent_supported(int(row), int(rank)))
+
+
+def attention_latent_decode_ranges(device: torch.device, n_seqs: int, n_heads: int, max_kv_len: int, split_keys: int) -> tuple:
+    """``decode_ranges`` for csrc/attention_latent.cu on this device: one block an SM, a block for every 16 heads."""
+    return decode_ranges(sm_count(device), n_seqs * ((n_heads + 15) // 16), max_kv_len, split_keys)
+
+
+def attention_latent(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seqs: int, max_q: int, n_heads: int, row: int,
+                     rank: int, scale: float, seq_qstart: torch.Tensor, seq_past: torch.Tensor, seq_slot: torch.Tensor,
+                     page_table: torch.Tensor, num_pages: int, pages: torch.Tensor, scratch: Optional[torch.Tensor],
+                     split_keys: int, max_splits: int, status: torch.Tensor, min_range_keys: int = 0) -> None:
+    """Causal attention of ``q [n, n_heads * row]`` over the cached rows ``pages [pages, 1, 64, row]`` taken as one kv head
+    whose values are the rows' leading ``rank`` features; ``out [n, n_heads * rank]``.  bfloat16, on the tensor cores.
+    Decode: ``scratch`` of ``attention_generic_scratch_floats(n_seqs, n_heads, rank, max_splits)`` floats; with
+    ``split_keys`` 0 a sequence's keys are shared out evenly over ``max_splits`` ranges of at least ``min_range_keys``."""
+    _need(q.stride(-1) == 1 and out.stride(-1) == 1 and pages.is_contiguous(), "attention: rows must be contiguous")
+    _need(q.dtype == out.dtype == pages.dtype == torch.bfloat16, "attention_latent: bfloat16 tensors only")
+    _need(pages.shape[-1] == row and pages.shape[-2] == 64, "attention_latent: pages of 64 rows of `row` features")
+    check(library().pe_attention_latent(
+        1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, row, rank, float(scale),
+        _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages),
+        _ptr(scratch), split_keys, max_splits, int(min_range_keys), _ptr(status), _stream()), "attention_latent")
+    _count(2 if decode else 1)
+
+
 def gemm_smallm_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
     """Whether csrc/gemm_smallm.cu takes ``x [M, K] @ weight [N, K]^T``: bfloat16, M <= 16, K % 8 == 0."""
     return (x.dtype == torch.bfloat16 and weight.dtype == torch.bfloat16 and x.dim() == 2 and x.shape[0] <= 16

@@ -37,10 +37,25 @@ def maps_first(w: torch.Tensor, heads: int, d: int) -> torch.Tensor:
 
 
 def attend_maps(ops, decode, q, maps, n_seqs, max_q, n_heads, n_kv_heads, d, dv, scale, chunk, seq_qstart, seq_past, seq_slot,
-                page_table, num_pages, k_pages, v_pages, status, max_kv_len, buffer) -> None:
+                page_table, num_pages, k_pages, v_pages, status, max_kv_len, buffer, tensor_cores=None) -> None:
     """Both softmax maps of every head as one grouped-query attention: ``q [n, 2 * n_heads * d]`` ([map][head][d]) over
     ``k_pages [pages, 2 * n_kv_heads, 64, d]`` and ``v_pages [pages, n_kv_heads, 64, dv]`` into ``maps [n, 2 * n_heads * dv]``
-    float32.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step."""
+    float32.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step.
+    ``tensor_cores``: None takes the tensor-core kernels where they take the shape (bfloat16, keys and values of one size,
+    64 or 128, groups up to 16); False keeps the float32-arithmetic kernels."""
+    if tensor_cores is None:
+        tensor_cores = q.is_cuda and d == dv and ops.attention_mma_supported(q.dtype, d, 2 * n_heads, 2 * n_kv_heads)
+    if tensor_cores:
+        scratch, split_keys, max_splits, floor = None, SPLIT_KEYS, 0, 0
+        if decode:
+            split_keys, max_splits, floor = ops.attention_mma_decode_ranges(q.device, d, n_seqs, 2 * n_kv_heads, int(max_kv_len),
+                                                                            SPLIT_KEYS)
+            scratch = buffer("attn.scratch", (ops.attention_generic_scratch_floats(n_seqs, 2 * n_heads, dv, max_splits),),
+                             torch.float32)
+        ops.attention_mma_masked(decode, q, maps, n_seqs, max_q, 2 * n_heads, 2 * n_kv_heads, d, scale, seq_qstart, seq_past,
+                                 seq_slot, page_table, num_pages, k_pages, v_pages, scratch, split_keys, max_splits, status,
+                                 min_range_keys=floor, chunk=chunk, v_heads=n_kv_heads, split_p=True)
+        return
     scratch, max_splits = None, 0
     if decode:
         max_splits = max(1, -(-int(max_kv_len) // SPLIT_KEYS))
@@ -118,7 +133,7 @@ class DiffAttention:
         maps = ctx.buffer("diff.maps", (n, 2 * nh * dv), torch.float32)   # the two maps stay float32 up to their difference
         attend_maps(ops, ctx.decode, qkv, maps, ctx.n_seqs, ctx.max_q, nh, nkv, d, dv, self.scale, self.chunk, ctx.seq_qstart,
                     ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages, view.v_pages, rt.status,
-                    ctx.max_kv_len, ctx.buffer)
+                    ctx.max_kv_len, ctx.buffer, tensor_cores=False if getattr(rt, "generic_attention", False) else None)
         heads = ctx.buffer("diff.heads", (n, nh * dv), rt.dtype)
         ops.diff_combine(maps, heads, nh, dv, self.lam, self.eps, 1.0 - self.diff)
         delta = ctx.buffer("diff.delta", (n, self.hidden), rt.dtype)

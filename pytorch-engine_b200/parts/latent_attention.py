@@ -29,11 +29,28 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
+LATENT_SPLIT_KEYS = 128   # keys per partial result of the tensor-core decode kernel while one wave of blocks holds them
+
+
 def attend_rows(ops, decode, qfull, mixed, n_seqs, max_q, n_heads, row, rank, scale, seq_qstart, seq_past, seq_slot, page_table,
-                num_pages, pages, status, max_kv_len, buffer) -> None:
+                num_pages, pages, status, max_kv_len, buffer, tensor_cores=None) -> None:
     """Every head's query of ``row`` features (``qfull [n, n_heads * row]``) over the cached rows ``pages [pages, 1, 64, row]``
     as one kv head whose values are the rows' leading ``rank`` features; ``mixed [n, n_heads * rank]`` gets the weighted
-    rows.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step."""
+    rows.  ``buffer(name, shape, dtype)`` hands out the step's scratch; ``max_kv_len``: the longest sequence of the step.
+    ``tensor_cores``: None takes the tensor-core kernels where they take the shape (bfloat16, rows in steps of 64 up to
+    576, values of 128, 256 or 512 features); False keeps the float32-arithmetic kernels."""
+    if tensor_cores is None:
+        tensor_cores = qfull.is_cuda and ops.attention_latent_supported(qfull.dtype, row, rank)
+    if tensor_cores:
+        scratch, split_keys, max_splits, floor = None, 0, 0, 0
+        if decode:
+            split_keys, max_splits, floor = ops.attention_latent_decode_ranges(qfull.device, n_seqs, n_heads, int(max_kv_len),
+                                                                               LATENT_SPLIT_KEYS)
+            scratch = buffer("attn.scratch", (ops.attention_generic_scratch_floats(n_seqs, n_heads, rank, max_splits),),
+                             torch.float32)
+        ops.attention_latent(decode, qfull, mixed, n_seqs, max_q, n_heads, row, rank, scale, seq_qstart, seq_past, seq_slot,
+                             page_table, num_pages, pages, scratch, split_keys, max_splits, status, min_range_keys=floor)
+        return
     scratch, max_splits = None, 0
     if decode:
         max_splits = max(1, -(-int(max_kv_len) // SPLIT_KEYS))
@@ -134,7 +151,7 @@ class LatentAttention:
         mixed = ctx.buffer("latent.mixed", (n, nh, r), rt.dtype)
         attend_rows(ops, ctx.decode, qfull.view(n, nh * row), mixed.view(n, nh * r), ctx.n_seqs, ctx.max_q, nh, row, r, self.scale,
                     ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, pages, rt.status, ctx.max_kv_len,
-                    ctx.buffer)
+                    ctx.buffer, tensor_cores=False if getattr(rt, "generic_attention", False) else None)
         # expand with W_uv head by head: [heads, n, rank] x [heads, rank, dv]
         heads_t = ctx.buffer("latent.heads_t", (nh, n, dv), rt.dtype)
         rt.batched_linear(mixed.transpose(0, 1), self.uv_t.transpose(1, 2), heads_t)

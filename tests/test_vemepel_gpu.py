@@ -480,6 +480,153 @@ def test_latent_rows_and_turned_queries(ops, dtype, rot):
         at += m
 
 
+def _starts_and_pasts(lens, q_lens):
+    qstart = [0]
+    for n in q_lens:
+        qstart.append(qstart[-1] + n)
+    return _i32(qstart), _i32([L - n for L, n in zip(lens, q_lens)])
+
+
+@pytest.mark.parametrize("row,r,nh", [(128, 128, 5), (192, 128, 16), (320, 256, 20), (576, 512, 3), (576, 512, 33)])
+def test_cached_rows_on_the_tensor_cores(ops, row, r, nh):
+    """The tensor-core kernels over cached rows whose leading features are the values: prompts that start at a page's
+    border, in its middle and at position 0, one token, and decoding with more heads than one block takes; one head looks
+    700 positions back.  Against the plain softmax on the same bfloat16 inputs."""
+    dtype = torch.bfloat16
+    assert ops.attention_latent_supported(dtype, row, r)
+    lens, q_lens = [900, 65, 300, 192], [130, 65, 1, 64]
+    g = torch.Generator().manual_seed(row + nh)
+    pg = Paged(lens, 1, row, dtype, seed=2)
+    rows = [torch.randn(n, 1, row, generator=g) for n in lens]
+    mark = row - 3 if row > r else 7
+    rows[0][200, 0] = 0.0
+    rows[0][200, 0, mark] = 12.0
+    for b in range(len(lens)):
+        pg.put(b, rows[b])
+    scale = 1.5 / math.sqrt(row)
+    look = min(3, nh - 1)
+    for decode, ql in ((False, q_lens), (True, [1] * len(lens))):
+        n = sum(ql)
+        q = torch.randn(n, nh * row, generator=g)
+        q[ql[0] - 1, look * row:(look + 1) * row] = 0.0
+        q[ql[0] - 1, look * row + mark] = 32.0                # its score stands far above the random ones
+        out = torch.zeros(n, nh * r, dtype=dtype, device=DEV)
+        qstart, past = _starts_and_pasts(lens, ql)
+        st = _status()
+        scratch, split_keys, splits, floor = None, 0, 0, 0
+        if decode:
+            split_keys, splits, floor = ops.attention_latent_decode_ranges(torch.device(DEV), len(lens), nh, max(lens), 128)
+            scratch = torch.zeros(ops.attention_generic_scratch_floats(len(lens), nh, r, splits), device=DEV)
+        ops.attention_latent(decode, q.to(dtype).to(DEV), out, len(lens), max(ql), nh, row, r, scale, qstart, past, pg.seq_slot,
+                             pg.table, pg.num_pages, pg.pages.view(pg.num_pages, 1, 64, row), scratch, split_keys, splits, st,
+                             min_range_keys=floor)
+        assert st.tolist()[0] == 0
+        at = 0
+        for b, (L, m) in enumerate(zip(lens, ql)):
+            keys = rows[b][:, 0].to(dtype).double()
+            pos = torch.arange(L - m, L)
+            visible = torch.arange(L)[None, :] <= pos[:, None]
+            for h in range(nh):
+                qh = q[at:at + m, h * row:(h + 1) * row].to(dtype).double()
+                want = plain.softmax_attend(qh, keys, keys[:, :r], scale, visible)
+                got = out[at:at + m, h * r:(h + 1) * r].double().cpu()
+                assert (got - want).abs().max() < 2e-2, (decode, b, h, float((got - want).abs().max()))
+            at += m
+        far = out[ql[0] - 1, look * r:(look + 1) * r].double().cpu()
+        assert (far - rows[0][200, 0, :r].to(dtype).double()).abs().max() < 7e-2   # bfloat16 steps of 1/16 at 12
+
+
+@pytest.mark.parametrize("d", [64, 128])
+@pytest.mark.parametrize("chunk", [0, 37, 64, 130])
+def test_two_key_maps_and_chunks_on_the_tensor_cores(ops, d, chunk):
+    """The tensor-core kernels with twice the key heads over one set of value heads, the chunk mask and a float32
+    output, weights in two bfloat16 terms: prompts that start inside a chunk, one token, decoding.  Against the plain
+    softmax on the same bfloat16 inputs; the weights' second term shows in the tolerance."""
+    dtype = torch.bfloat16
+    nh, nkv, nv = 12, 4, 2
+    assert ops.attention_mma_supported(dtype, d, nh, nkv)
+    lens, q_lens = [700, 65, 300, 131], [135, 65, 1, 2]
+    g = torch.Generator().manual_seed(d + chunk)
+    kp, vp = Paged(lens, nkv, d, dtype, seed=3), Paged(lens, nv, d, dtype, seed=3)
+    ks = [torch.randn(n, nkv, d, generator=g) for n in lens]
+    vs = [torch.randn(n, nv, d, generator=g) for n in lens]
+    for b in range(len(lens)):
+        kp.put(b, ks[b])
+        vp.put(b, vs[b])
+    scale = 1.5 / math.sqrt(d)
+    for decode, ql in ((False, q_lens), (True, [1] * len(lens))):
+        n = sum(ql)
+        q = torch.randn(n, nh * d, generator=g)
+        for split_p, tol in ((True, 2e-4), (False, 2e-2)):
+            out = torch.zeros(n, nh * d, device=DEV)
+            qstart, past = _starts_and_pasts(lens, ql)
+            st = _status()
+            scratch, split_keys, splits, floor = None, 512, 0, 0
+            if decode:
+                split_keys, splits, floor = ops.attention_mma_decode_ranges(torch.device(DEV), d, len(lens), nkv, max(lens), 512)
+                scratch = torch.zeros(ops.attention_generic_scratch_floats(len(lens), nh, d, splits), device=DEV)
+            ops.attention_mma_masked(decode, q.to(dtype).to(DEV), out, len(lens), max(ql), nh, nkv, d, scale, qstart, past,
+                                     kp.seq_slot, kp.table, kp.num_pages, kp.pages, vp.pages, scratch, split_keys, splits, st,
+                                     min_range_keys=floor, chunk=chunk, v_heads=nv, split_p=split_p)
+            assert st.tolist()[0] == 0
+            at = 0
+            for b, (L, m) in enumerate(zip(lens, ql)):
+                pos = torch.arange(L - m, L)
+                j = torch.arange(L)
+                visible = j[None, :] <= pos[:, None]
+                if chunk:
+                    visible &= (j[None, :] // chunk) == (pos[:, None] // chunk)
+                for h in range(nh):
+                    kv = h // (nh // nkv)
+                    want = plain.softmax_attend(q[at:at + m, h * d:(h + 1) * d].to(dtype).double(),
+                                                ks[b][:, kv].to(dtype).double(), vs[b][:, kv % nv].to(dtype).double(), scale, visible)
+                    err = float((out[at:at + m, h * d:(h + 1) * d].double().cpu() - want).abs().max())
+                    assert err < tol, (decode, split_p, b, h, err)
+                at += m
+
+
+@pytest.mark.parametrize("chunk", [37, 64, 130])
+def test_chunk_edges_on_the_tensor_cores(ops, chunk):
+    """One key matches the query strongly: at the first position of the query's own block it takes all the weight, one
+    position earlier it is not seen.  Queries at a block's first, second and last position and around page borders."""
+    dtype = torch.bfloat16
+    d, nh, nkv = 64, 2, 1
+    length = 3 * chunk + 70
+    for qpos in sorted({chunk, chunk + 1, 2 * chunk - 1, 2 * chunk, 3 * chunk + 5, 128, 129, 191, 192, length - 1}):
+        start = qpos // chunk * chunk
+        for key_at, seen in ((start, True), (start - 1, False)):
+            if key_at < 0:
+                continue
+            for decode in (False, True):
+                k = torch.zeros(qpos + 1, nkv, d)
+                k[key_at, 0, 0] = 30.0
+                g = torch.Generator().manual_seed(qpos)
+                v = torch.randn(qpos + 1, nkv, d, generator=g)
+                kp, vp = Paged([qpos + 1], nkv, d, dtype, seed=1), Paged([qpos + 1], nkv, d, dtype, seed=1)
+                kp.put(0, k)
+                vp.put(0, v)
+                q_len = 1 if decode else min(qpos + 1, 9)
+                q = torch.zeros(q_len, nh * d)
+                q[-1, 0] = 1.0
+                q[-1, d] = 1.0
+                out = torch.zeros(q_len, nh * d, device=DEV)
+                qstart, past = _starts_and_pasts([qpos + 1], [q_len])
+                st = _status()
+                scratch, split_keys, splits, floor = None, 512, 0, 0
+                if decode:
+                    split_keys, splits, floor = ops.attention_mma_decode_ranges(torch.device(DEV), d, 1, nkv, qpos + 1, 512)
+                    scratch = torch.zeros(ops.attention_generic_scratch_floats(1, nh, d, splits), device=DEV)
+                ops.attention_mma_masked(decode, q.to(dtype).to(DEV), out, 1, q_len, nh, nkv, d, 1.0, qstart, past, kp.seq_slot,
+                                         kp.table, kp.num_pages, kp.pages, vp.pages, scratch, split_keys, splits, st,
+                                         min_range_keys=floor, chunk=chunk, split_p=True)
+                assert st.tolist()[0] == 0
+                vq = v.to(dtype).double()
+                want = vq[key_at, 0] if seen else vq[start:qpos + 1, 0].mean(0)
+                got = out[-1].double().cpu().view(nh, d)
+                for h in range(nh):
+                    assert (got[h] - want).abs().max() < 1e-3, (chunk, qpos, key_at, decode)
+
+
 # ---- every mechanism alone, as a model of one layer ---------------------------------------------------------------
 ONE_LAYER = {
     "latent, one gate a head": _layer(_latent(3, 20, 28, 36, 0.2), None),
@@ -489,6 +636,10 @@ ONE_LAYER = {
     "two maps, chunk 33, groups of 3": _layer(_diff(6, 2, 24, 8, 0.2, 0.5, size=33), None),
     "two maps, no mask, one kv head": _layer(_diff(4, 1, 8, 72, 0.4, 0.8), None),
     "two maps, chunk of two pages": _layer(_diff(2, 2, 40, 40, 0.15, 0.1, size=128), None),
+    "latent, rows the tensor cores take": _layer(_latent(2, 16, 24, 128, 0.2), None),
+    "latent with a turned part, rows the tensor cores take": _layer(_latent(3, 16, 16, 128, 0.2, rot_dim=64, dims=64, base=300.0),
+                                                                   None),
+    "two maps, chunk 33, heads the tensor cores take": _layer(_diff(4, 2, 64, 64, 0.12, 0.5, size=33), None),
     "dense": _layer(_diff(1, 1, 8, 8, 0.3, 0.5), _dense(90)),
     "one expert of seven": _layer(_latent(1, 8, 8, 8, 0.3), _moe(7, 1, 24)),
     "every expert": _layer(_latent(1, 8, 8, 8, 0.3), _moe(4, 4, 40)),
