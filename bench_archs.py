@@ -553,9 +553,8 @@ def vemepel_kernel_pairs(pe, torch, s, peaks, prompt, batch, context):
         kv_rows = torch.randn(n, 3 * G * d, device=dev).to(bf)
 
         def append():
-            ops.rows_to_pages(kv_rows, 0, 2 * G, d, token_seq, token_pos, slots, table, n_pages, kp2, status)
-            ops.rows_to_pages(kv_rows, 2 * G * d, G, d, token_seq, token_pos, slots, table, n_pages, vp, status)
-        entry(f"{what}: two key maps and the values into their pages (2 kernels)", us_of(append), roof_us(n * 3 * G * d * 4),
+            ops.rows_to_pages_pair(kv_rows, 0, 2 * G, d, kp2, 2 * G * d, G, d, vp, token_seq, token_pos, slots, table, n_pages, status)
+        entry(f"{what}: two key maps and the values into their pages", us_of(append), roof_us(n * 3 * G * d * 4),
               "qk_norm_rope_append", us_like, roof_us(n * (H + 2 * G) * d * 2 + n * (H + G) * d * 2 + n * 2 * G * d * 2))
         # ---- gates, norms and the stream
         heads_t = torch.randn(H, n, d, device=dev).to(bf)

@@ -89,6 +89,9 @@ int pe_diff_combine(int dtype, const float* a, void* out, int n_tokens, int head
 int pe_rows_to_pages(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int n_tokens,
     const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table, int table_stride,
     int num_pages, void* pages, int* status, cudaStream_t stream);
+int pe_rows_to_pages_pair(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int col0_b, int heads_b,
+    int dim_b, int n_tokens, const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table,
+    int table_stride, int num_pages, void* pages, void* pages_b, int* status, cudaStream_t stream);
 int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q_col0, int low_col0, int heads, int d, int dr,
     int rank, const float* norm_w, float eps, const float* cos_t, const float* sin_t, int rot, int table_rows,
     int n_tokens, const int* token_seq, const int* token_pos, const int* seq_slot, const int* page_table,

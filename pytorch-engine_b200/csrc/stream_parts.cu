@@ -57,6 +57,76 @@ __global__ void __launch_bounds__(256) norm_token_shift_kernel(const float* x, c
   }
 }
 
+__device__ __forceinline__ void store4(float* dst, float a, float b, float c, float d) {
+  *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+__device__ __forceinline__ void store4(__nv_bfloat16* dst, float a, float b, float c, float d) {
+  const __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+  *reinterpret_cast<uint2*>(dst) = make_uint2(*reinterpret_cast<const uint32_t*>(&lo), *reinterpret_cast<const uint32_t*>(&hi));
+}
+
+// The same for rows that a block holds in registers (width a multiple of 4, at most 4 * VPT * 256): every global read
+// is issued before the first reduction, and each row is read once.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(256) norm_token_shift_rows_kernel(const float* x, const float* __restrict__ w, float eps,
+                                                                    const float* __restrict__ mix, float* state,
+                                                                    const int* token_seq, const int* seq_slot,
+                                                                    const int* seq_qstart, T* __restrict__ out, int n_tokens,
+                                                                    int width, int n_slots, int* status) {
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int t = blockIdx.x;
+  const int b = token_seq[t];
+  const bool first = t == seq_qstart[b];
+  const int slot = seq_slot[b];
+  if (first && (slot < 0 || slot >= n_slots)) {
+    if (threadIdx.x == 0) report(status, kStatusSlotOutOfRange, t, slot, n_slots);
+    return;
+  }
+  const int nv = width >> 2;
+  const float4* cur = reinterpret_cast<const float4*>(x + (size_t)t * width);
+  const float4* other = first ? reinterpret_cast<const float4*>(x + (size_t)(seq_qstart[b + 1] - 1) * width) : cur - nv;
+  const float4* w4 = reinterpret_cast<const float4*>(w);
+  const float4* m4 = reinterpret_cast<const float4*>(mix);
+  float4* kept4 = reinterpret_cast<float4*>(state + (size_t)(first ? slot : 0) * width);
+  const float4 zero = make_float4(0.f, 0.f, 0.f, 0.f);
+  float4 a[VPT], o[VPT], wv[VPT], mv[VPT], kp[VPT];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * 256;
+    const bool in = c < nv;
+    a[k] = in ? cur[c] : zero;
+    o[k] = in ? other[c] : zero;
+    wv[k] = in ? w4[c] : zero;
+    mv[k] = in ? m4[c] : zero;
+    kp[k] = (in && first) ? kept4[c] : zero;
+  }
+  float s0 = 0.f, s1 = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    s0 = fmaf(a[k].x, a[k].x, fmaf(a[k].y, a[k].y, fmaf(a[k].z, a[k].z, fmaf(a[k].w, a[k].w, s0))));
+    s1 = fmaf(o[k].x, o[k].x, fmaf(o[k].y, o[k].y, fmaf(o[k].z, o[k].z, fmaf(o[k].w, o[k].w, s1))));
+  }
+  s0 = block_sum(s0, red);
+  s1 = block_sum(s1, red);
+  const float inv0 = rsqrtf(s0 / (float)width + eps), inv1 = rsqrtf(s1 / (float)width + eps);
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * 256;
+    if (c >= nv) continue;
+    const float4 h = make_float4(a[k].x * inv0 * wv[k].x, a[k].y * inv0 * wv[k].y, a[k].z * inv0 * wv[k].z, a[k].w * inv0 * wv[k].w);
+    const float4 ho = make_float4(o[k].x * inv1 * wv[k].x, o[k].y * inv1 * wv[k].y, o[k].z * inv1 * wv[k].z, o[k].w * inv1 * wv[k].w);
+    float4 hp = ho;
+    if (first) {
+      hp = kp[k];       // read above, before this thread (alone) replaces it
+      kept4[c] = ho;
+    }
+    store4(out + (size_t)t * width + 4 * c, fmaf(hp.x - h.x, mv[k].x, h.x), fmaf(hp.y - h.y, mv[k].y, h.y),
+           fmaf(hp.z - h.z, mv[k].z, h.z), fmaf(hp.w - h.w, mv[k].w, h.w));
+  }
+}
+
 __global__ void depth_average_kernel(const float* results, long long layer_stride, const float* __restrict__ coeff,
                                      int n_terms, float* __restrict__ out, float* __restrict__ copy, long long n) {
   pdl_wait_block();
@@ -93,6 +163,88 @@ __global__ void __launch_bounds__(256) polynorm_kernel(const T* z, const float* 
   for (int c = threadIdx.x; c < width; c += blockDim.x) {
     const float v = to_f32<T>(row[c]), v2 = v * v;
     out[(size_t)blockIdx.x * width + c] = from_f32<T>(fmaf(f1, v, fmaf(f2, v2, fmaf(f3, v2 * v, e))));
+  }
+}
+
+template <typename T> struct Vec16;
+template <> struct Vec16<float> {
+  static constexpr int N = 4;
+  __device__ static void load(const float* p, float (&v)[4]) {
+    const float4 q = *reinterpret_cast<const float4*>(p);
+    v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+  }
+  __device__ static void store(float* p, const float (&v)[4]) { *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]); }
+};
+template <> struct Vec16<__nv_bfloat16> {
+  static constexpr int N = 8;
+  __device__ static void load(const __nv_bfloat16* p, float (&v)[8]) {
+    const uint4 q = *reinterpret_cast<const uint4*>(p);
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float2 f = __bfloat1622float2(h[i]);
+      v[2 * i] = f.x; v[2 * i + 1] = f.y;
+    }
+  }
+  __device__ static void store(__nv_bfloat16* p, const float (&v)[8]) {
+    uint4 q;
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&q);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) h[i] = __floats2bfloat162_rn(v[2 * i], v[2 * i + 1]);
+    *reinterpret_cast<uint4*>(p) = q;
+  }
+};
+
+// The same for rows that a block holds in registers (rows of whole 16-byte vectors, at most VPT a thread): the row is
+// read once.  grid: rows; block: any multiple of 32 threads.
+template <typename T, int VPT>
+__global__ void __launch_bounds__(1024) polynorm_rows_kernel(const T* z, const float* __restrict__ coeff, float eps,
+                                                             T* __restrict__ out, int width) {
+  __shared__ float red[32];
+  pdl_wait_block();
+  pdl_launch_dependents();
+  constexpr int N = Vec16<T>::N;
+  const int nv = width / N;
+  const T* row = z + (size_t)blockIdx.x * width;
+  float v[VPT][N];
+  float s1 = 0.f, s2 = 0.f, s3 = 0.f;
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c < nv) {
+      Vec16<T>::load(row + (size_t)c * N, v[k]);
+    } else {
+#pragma unroll
+      for (int i = 0; i < N; ++i) v[k][i] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float u = v[k][i], u2 = u * u, u3 = u2 * u;
+      s1 = fmaf(u, u, s1);
+      s2 = fmaf(u2, u2, s2);
+      s3 = fmaf(u3, u3, s3);
+    }
+  }
+  s1 = block_sum(s1, red);
+  s2 = block_sum(s2, red);
+  s3 = block_sum(s3, red);
+  const float n = (float)width;
+  const float f1 = coeff[0] * rsqrtf(s1 / n + eps), f2 = coeff[1] * rsqrtf(s2 / n + eps), f3 = coeff[2] * rsqrtf(s3 / n + eps);
+  const float e = coeff[3];
+#pragma unroll
+  for (int k = 0; k < VPT; ++k) {
+    const int c = threadIdx.x + k * blockDim.x;
+    if (c >= nv) continue;
+    float r[N];
+#pragma unroll
+    for (int i = 0; i < N; ++i) {
+      const float u = v[k][i], u2 = u * u;
+      r[i] = fmaf(f1, u, fmaf(f2, u2, fmaf(f3, u2 * u, e)));
+    }
+    Vec16<T>::store(out + (size_t)blockIdx.x * width + (size_t)c * N, r);
   }
 }
 
@@ -153,11 +305,13 @@ __device__ __forceinline__ long long page_row(int t, const int* token_seq, const
   return (long long)page * kPageTokens + (pos % kPageTokens);
 }
 
-// pages: [num_pages, heads, 64, dim]; src row t holds heads * dim features from column col0.  grid: tokens.
+// pages: [num_pages, heads, 64, dim]; src row t holds heads * dim features from column col0.  A second set (col0_b,
+// heads_b, dim_b, pages_b; pages_b null: none) goes to the same page numbers of its own pool.  grid: tokens.
 template <typename T>
-__global__ void rows_to_pages_kernel(const T* src, long long src_ld, int col0, int heads, int dim, const int* token_seq,
-                                     const int* token_pos, const int* seq_slot, const int* page_table, int table_stride,
-                                     int num_pages, T* __restrict__ pages, int* status) {
+__global__ void rows_to_pages_kernel(const T* src, long long src_ld, int col0, int heads, int dim, int col0_b, int heads_b,
+                                     int dim_b, const int* token_seq, const int* token_pos, const int* seq_slot,
+                                     const int* page_table, int table_stride, int num_pages, T* __restrict__ pages,
+                                     T* __restrict__ pages_b, int* status) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int t = blockIdx.x;
@@ -168,6 +322,12 @@ __global__ void rows_to_pages_kernel(const T* src, long long src_ld, int col0, i
   for (int i = threadIdx.x; i < heads * dim; i += blockDim.x) {
     const int h = i / dim, c = i - h * dim;
     pages[(((size_t)page * heads + h) * kPageTokens + r) * dim + c] = row[i];
+  }
+  if (pages_b == nullptr) return;
+  const T* row_b = src + (size_t)t * src_ld + col0_b;
+  for (int i = threadIdx.x; i < heads_b * dim_b; i += blockDim.x) {
+    const int h = i / dim_b, c = i - h * dim_b;
+    pages_b[(((size_t)page * heads_b + h) * kPageTokens + r) * dim_b + c] = row_b[i];
   }
 }
 
@@ -259,8 +419,17 @@ extern "C" int pe_norm_token_shift(int out_dtype, const float* x, const float* w
                                    int width, int n_slots, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (width <= 0 || n_slots <= 0) return PE_ERR_BAD_ARGUMENT;
-  PE_BY_DTYPE(out_dtype, pe::launch(pe::norm_token_shift_kernel<T>, n_tokens, 256, 0, stream, x, w, eps, mix, state, token_seq,
-                                    seq_slot, seq_qstart, (T*)out, n_tokens, width, n_slots, status));
+  const bool vec = width % 4 == 0 && width <= 8192 && ((uintptr_t)x % 16) == 0 && ((uintptr_t)w % 16) == 0 &&
+                   ((uintptr_t)mix % 16) == 0 && ((uintptr_t)state % 16) == 0 && ((uintptr_t)out % 16) == 0;
+#define PE_NTS(KERNEL)                                                                                                     \
+  PE_BY_DTYPE(out_dtype, pe::launch(KERNEL, n_tokens, 256, 0, stream, x, w, eps, mix, state, token_seq, seq_slot, seq_qstart, \
+                                    (T*)out, n_tokens, width, n_slots, status))
+  if (!vec) { PE_NTS(pe::norm_token_shift_kernel<T>); }
+  else if (width <= 1024) { PE_NTS((pe::norm_token_shift_rows_kernel<T, 1>)); }
+  else if (width <= 2048) { PE_NTS((pe::norm_token_shift_rows_kernel<T, 2>)); }
+  else if (width <= 4096) { PE_NTS((pe::norm_token_shift_rows_kernel<T, 4>)); }
+  else { PE_NTS((pe::norm_token_shift_rows_kernel<T, 8>)); }
+#undef PE_NTS
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -279,7 +448,21 @@ extern "C" int pe_polynorm(int dtype, const void* z, const float* coeff, float e
                            cudaStream_t stream) {
   if (n_rows <= 0) return PE_OK;
   if (width <= 0) return PE_ERR_BAD_ARGUMENT;
-  PE_BY_DTYPE(dtype, pe::launch(pe::polynorm_kernel<T>, n_rows, 256, 0, stream, (const T*)z, coeff, eps, (T*)out, width));
+  const int per_vec = dtype == PE_F32 ? 4 : 8;
+  const int nv = width / per_vec;
+  // few rows: as many threads a row as it has vectors (one pass of loads in flight); many rows: 256 threads
+  int threads = n_rows <= 2 * pe::kSMs ? (nv + 31) / 32 * 32 : 256;
+  if (threads > 1024) threads = 1024;
+  if (threads < 32) threads = 32;
+  const int vpt = (nv + threads - 1) / threads;
+  const bool vec = width % per_vec == 0 && vpt <= 4 && ((uintptr_t)z % 16) == 0 && ((uintptr_t)out % 16) == 0;
+#define PE_PN(KERNEL, THREADS) \
+  PE_BY_DTYPE(dtype, pe::launch(KERNEL, n_rows, THREADS, 0, stream, (const T*)z, coeff, eps, (T*)out, width))
+  if (!vec) { PE_PN(pe::polynorm_kernel<T>, 256); }
+  else if (vpt <= 1) { PE_PN((pe::polynorm_rows_kernel<T, 1>), threads); }
+  else if (vpt <= 2) { PE_PN((pe::polynorm_rows_kernel<T, 2>), threads); }
+  else { PE_PN((pe::polynorm_rows_kernel<T, 4>), threads); }
+#undef PE_PN
   PE_LAUNCH_CHECK();
   return PE_OK;
 }
@@ -313,8 +496,22 @@ extern "C" int pe_rows_to_pages(int dtype, const void* src, long long src_ld, in
                                 int table_stride, int num_pages, void* pages, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (heads <= 0 || dim <= 0 || col0 < 0) return PE_ERR_BAD_ARGUMENT;
+  return pe_rows_to_pages_pair(dtype, src, src_ld, col0, heads, dim, 0, 0, 0, n_tokens, token_seq, token_pos, seq_slot,
+                               page_table, table_stride, num_pages, pages, nullptr, status, stream);
+}
+
+// Two column ranges of the same rows into two pools that share their page numbers (keys and values) in one launch;
+// pages_b null: only the first.
+extern "C" int pe_rows_to_pages_pair(int dtype, const void* src, long long src_ld, int col0, int heads, int dim, int col0_b,
+                                     int heads_b, int dim_b, int n_tokens, const int* token_seq, const int* token_pos,
+                                     const int* seq_slot, const int* page_table, int table_stride, int num_pages,
+                                     void* pages, void* pages_b, int* status, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (heads <= 0 || dim <= 0 || col0 < 0) return PE_ERR_BAD_ARGUMENT;
+  if (pages_b && (heads_b <= 0 || dim_b <= 0 || col0_b < 0)) return PE_ERR_BAD_ARGUMENT;
   PE_BY_DTYPE(dtype, pe::launch(pe::rows_to_pages_kernel<T>, n_tokens, 128, 0, stream, (const T*)src, src_ld, col0, heads, dim,
-                                token_seq, token_pos, seq_slot, page_table, table_stride, num_pages, (T*)pages, status));
+                                col0_b, heads_b, dim_b, token_seq, token_pos, seq_slot, page_table, table_stride, num_pages,
+                                (T*)pages, (T*)pages_b, status));
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

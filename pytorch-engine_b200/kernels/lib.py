@@ -98,6 +98,7 @@ _SIGNATURES = {
     "pe_sigmoid_gate": [I, P, L, L, P, L, P, L, I, I, I, I, P],
     "pe_diff_combine": [I, P, P, I, I, I, F, F, F, P],
     "pe_rows_to_pages": [I, P, L, I, I, I, I, P, P, P, P, I, I, P, P, P],
+    "pe_rows_to_pages_pair": [I, P, L, I, I, I, I, I, I, I, P, P, P, P, I, I, P, P, P, P],
     "pe_latent_prepare": [I, P, L, I, I, I, I, I, I, P, F, P, P, I, I, I, P, P, P, P, I, I, P, P, P, I, P, P],
 }
 _RESTYPES = {"pe_wait_limit_polls": (L, []),

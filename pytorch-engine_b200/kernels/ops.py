@@ -881,6 +881,22 @@ def rows_to_pages(src: torch.Tensor, col0: int, heads: int, dim: int, token_seq:
     _count(1)
 
 
+def rows_to_pages_pair(src: torch.Tensor, col0: int, heads: int, dim: int, pages: torch.Tensor, col0_b: int, heads_b: int,
+                        dim_b: int, pages_b: torch.Tensor, token_seq: torch.Tensor, token_pos: torch.Tensor,
+                        seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, status: torch.Tensor) -> None:
+    """``rows_to_pages`` for two column ranges of the same rows at once (keys and values): the second range goes into
+    ``pages_b [num_pages, heads_b, 64, dim_b]``, a pool with the same page numbers."""
+    _need(src.stride(-1) == 1 and pages.is_contiguous() and pages_b.is_contiguous()
+          and src.dtype == pages.dtype == pages_b.dtype and col0 + heads * dim <= src.shape[1]
+          and col0_b + heads_b * dim_b <= src.shape[1] and pages.shape[0] == pages_b.shape[0] == num_pages,
+          "rows_to_pages_pair: shapes and dtypes")
+    check(library().pe_rows_to_pages_pair(dtype_tag(src.dtype), _ptr(src), src.stride(0), int(col0), heads, dim, int(col0_b),
+                                          heads_b, dim_b, src.shape[0], _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot),
+                                          _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages), _ptr(pages_b),
+                                          _ptr(status), _stream()), "rows_to_pages_pair")
+    _count(1)
+
+
 def latent_prepare(x: torch.Tensor, q_col0: int, low_col0: int, heads: int, d: int, dr: int, rank: int, norm_w: torch.Tensor,
                    eps: float, cos: Optional[torch.Tensor], sin: Optional[torch.Tensor], rot: int, token_seq: torch.Tensor,
                    token_pos: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,

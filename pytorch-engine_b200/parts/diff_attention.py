@@ -128,8 +128,8 @@ class DiffAttention:
         rt.linear(x, self.qkv, out=qkv)
         where = (ctx.token_seq, ctx.token_pos, ctx.seq_slot, view.page_table, view.num_pages)
         if writes_cache:
-            ops.rows_to_pages(qkv, self.q_cols, 2 * nkv, d, *where, view.k_pages, rt.status)
-            ops.rows_to_pages(qkv, self.q_cols + self.k_cols, nkv, dv, *where, view.v_pages, rt.status)
+            ops.rows_to_pages_pair(qkv, self.q_cols, 2 * nkv, d, view.k_pages, self.q_cols + self.k_cols, nkv, dv, view.v_pages,
+                                   *where, rt.status)
         maps = ctx.buffer("diff.maps", (n, 2 * nh * dv), torch.float32)   # the two maps stay float32 up to their difference
         attend_maps(ops, ctx.decode, qkv, maps, ctx.n_seqs, ctx.max_q, nh, nkv, d, dv, self.scale, self.chunk, ctx.seq_qstart,
                     ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages, view.v_pages, rt.status,

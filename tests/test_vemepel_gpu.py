@@ -168,7 +168,7 @@ def _i32(x):
 
 # ---- mechanisms at kernel level ---------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [72, 256, 1030])
+@pytest.mark.parametrize("width", [72, 256, 1030, 1028, 2052, 5000, 8192, 8196])
 def test_norm_and_token_shift_with_kept_rows(ops, dtype, width):
     """Three sequences in one step (a continuing one, a new one, a single token) on slots that hold other rows; then a
     second step that continues all three: the kept row must be the unmoved last row, zeros for a new sequence."""
@@ -217,10 +217,11 @@ def test_depth_average_adds_the_terms_it_is_given(ops):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("width", [40, 320, 2050])
-def test_polynorm(ops, dtype, width):
+@pytest.mark.parametrize("rows", [19, 400])
+@pytest.mark.parametrize("width", [40, 320, 2050, 4104, 5000, 11000, 40000])
+def test_polynorm(ops, dtype, width, rows):
     g = torch.Generator().manual_seed(width)
-    z = (2.0 * torch.randn(19, width, generator=g)).to(dtype).to(DEV)
+    z = (2.0 * torch.randn(rows, width, generator=g)).to(dtype).to(DEV)
     coeff = torch.tensor([0.9, -0.4, 0.25, 0.3], device=DEV)
     out = torch.empty_like(z)
     ops.polynorm(z, coeff, 1e-5, out)
@@ -428,6 +429,29 @@ def test_two_key_maps_over_one_set_of_values(ops, dtype):
                                         vs[b][:, kv % nv].to(dtype).double(), 0.4, visible)
             assert (out[at:at + m, h * dv:(h + 1) * dv].double().cpu() - want).abs().max() < 1e-4
         at += m
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_keys_and_values_into_their_pages_at_once(ops, dtype):
+    """Two column ranges of the step's rows into two pools with the same page numbers: what two single copies write."""
+    lens, q_lens = [70, 130, 5], [9, 130, 1]
+    nk, dk, nv, dv = 4, 12, 2, 20
+    g = torch.Generator().manual_seed(11)
+    n = sum(q_lens)
+    x = torch.randn(n, 7 + nk * dk + nv * dv, generator=g).to(dtype).to(DEV)
+    pos = _i32(sum(([L - m + j for j in range(m)] for L, m in zip(lens, q_lens)), []))
+    token_seq = _i32(sum(([b] * m for b, m in enumerate(q_lens)), []))
+    single_k, single_v = Paged(lens, nk, dk, dtype, seed=9), Paged(lens, nv, dv, dtype, seed=9)
+    both_k, both_v = Paged(lens, nk, dk, dtype, seed=9), Paged(lens, nv, dv, dtype, seed=9)
+    st = _status()
+    where = (token_seq, pos, single_k.seq_slot, single_k.table, single_k.num_pages)
+    ops.rows_to_pages(x, 7, nk, dk, *where, single_k.pages, st)
+    ops.rows_to_pages(x, 7 + nk * dk, nv, dv, *where, single_v.pages, st)
+    ops.rows_to_pages_pair(x, 7, nk, dk, both_k.pages, 7 + nk * dk, nv, dv, both_v.pages, *where, st)
+    assert st.tolist()[0] == 0
+    assert torch.equal(single_k.pages, both_k.pages) and torch.equal(single_v.pages, both_v.pages)
+    page = int(single_k.table[single_k.slots[1], 1])
+    assert torch.equal(both_v.pages[page, 1, 3], x[9 + 64 + 3, 7 + nk * dk + dv:7 + nk * dk + 2 * dv])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
