@@ -76,11 +76,16 @@ __device__ __forceinline__ uint32_t tile_off(int r, int chunk, int rows) {
   return (uint32_t)((chunk >> 3) * (rows * 128) + r * 128 + (((chunk & 7) ^ (r & 7)) << 4));
 }
 
-// One elected thread starts the copy of the page that holds position k0 into a stage; `bar` counts the bytes.
-__device__ __forceinline__ void issue_page(const Args& a, const CUtensorMap* map, int slot, int k0, char* stage, uint64_t* bar) {
+// The page table's entry for the page that holds position k0 (-1 beyond the table).  The value is looked at only by
+// issue_page, one round later, so that the elected thread does not wait for the table while the others compute.
+__device__ __forceinline__ int lookup_page(const Args& a, int slot, int k0) {
   const int logical = k0 / BN;
-  int page = -1;
-  if (logical < a.table_stride) page = a.page_table[(size_t)slot * a.table_stride + logical];
+  return logical < a.table_stride ? a.page_table[(size_t)slot * a.table_stride + logical] : -1;
+}
+
+// One elected thread starts the copy of `page` (it holds position k0) into a stage; `bar` counts the bytes.
+__device__ __forceinline__ void issue_page(const Args& a, const CUtensorMap* map, int slot, int k0, int page, char* stage,
+                                           uint64_t* bar) {
   if (page < 0 || page >= a.num_pages) {
     report(a.status, kStatusPageOutOfRange, slot, page, k0);
     page = 0;
@@ -160,11 +165,13 @@ __global__ void __launch_bounds__(MB * KS * 32, 1) latent_kernel(Args a, const _
   const int slot = a.seq_slot[b];
   const int n_tiles = (k_hi - k_lo + BN - 1) / BN;
 
+  int page_next = -1;   // the elected thread's: the table's entry for the page after the one in flight
   if (tid == 0) {
     tma::mbar_init(&bars[0], 1);
     tma::mbar_init(&bars[1], 1);
     tma::fence_barrier_init();
-    issue_page(a, &map, slot, k_lo, smem, &bars[0]);
+    issue_page(a, &map, slot, k_lo, lookup_page(a, slot, k_lo), smem, &bars[0]);
+    if (n_tiles > 1) page_next = lookup_page(a, slot, k_lo + BN);
   }
   const int cpr = row / 8;   // 16-byte chunks of a query row
   for (int i = tid; i < M * cpr; i += THREADS) {
@@ -188,7 +195,10 @@ __global__ void __launch_bounds__(MB * KS * 32, 1) latent_kernel(Args a, const _
   for (int it = 0; it < n_tiles; ++it) {
     const int k0 = k_lo + it * BN;
     // next page into the other stage (everyone left it at the end of the last round)
-    if (tid == 0 && it + 1 < n_tiles) issue_page(a, &map, slot, k0 + BN, smem + ((it + 1) & 1) * stage_bytes, &bars[(it + 1) & 1]);
+    if (tid == 0 && it + 1 < n_tiles) {
+      issue_page(a, &map, slot, k0 + BN, page_next, smem + ((it + 1) & 1) * stage_bytes, &bars[(it + 1) & 1]);
+      if (it + 2 < n_tiles) page_next = lookup_page(a, slot, k0 + 2 * BN);
+    }
     if (!tma::mbar_wait(&bars[it & 1], (it >> 1) & 1)) {
       give_up(a, bars, 3);
       return;
@@ -198,6 +208,7 @@ __global__ void __launch_bounds__(MB * KS * 32, 1) latent_kernel(Args a, const _
     float s[NT][4];
 #pragma unroll
     for (int n = 0; n < NT; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+#pragma unroll 4   // rows come in steps of 64 features: the loads of four steps can be in flight ahead of their products
     for (int kk = 0; kk < row / 16; ++kk) {
       uint32_t qf[4];
       ldmatrix_x4(qf, q_base + tile_off(a_row, kk * 2 + (lane >> 4), M));
