@@ -432,34 +432,38 @@ def test_two_key_maps_over_one_set_of_values(ops, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_keys_and_values_into_their_pages_at_once(ops, dtype):
-    """Two column ranges of the step's rows into two pools with the same page numbers: what two single copies write."""
+@pytest.mark.parametrize("c0,dk,dv", [(7, 12, 20), (8, 16, 24)])
+def test_keys_and_values_into_their_pages_at_once(ops, dtype, c0, dk, dv):
+    """Two column ranges of the step's rows into two pools with the same page numbers: what two single copies write, and
+    the rows themselves."""
     lens, q_lens = [70, 130, 5], [9, 130, 1]
-    nk, dk, nv, dv = 4, 12, 2, 20
+    nk, nv = 4, 2
     g = torch.Generator().manual_seed(11)
     n = sum(q_lens)
-    x = torch.randn(n, 7 + nk * dk + nv * dv, generator=g).to(dtype).to(DEV)
+    x = torch.randn(n, c0 + nk * dk + nv * dv, generator=g).to(dtype).to(DEV)
     pos = _i32(sum(([L - m + j for j in range(m)] for L, m in zip(lens, q_lens)), []))
     token_seq = _i32(sum(([b] * m for b, m in enumerate(q_lens)), []))
     single_k, single_v = Paged(lens, nk, dk, dtype, seed=9), Paged(lens, nv, dv, dtype, seed=9)
     both_k, both_v = Paged(lens, nk, dk, dtype, seed=9), Paged(lens, nv, dv, dtype, seed=9)
     st = _status()
     where = (token_seq, pos, single_k.seq_slot, single_k.table, single_k.num_pages)
-    ops.rows_to_pages(x, 7, nk, dk, *where, single_k.pages, st)
-    ops.rows_to_pages(x, 7 + nk * dk, nv, dv, *where, single_v.pages, st)
-    ops.rows_to_pages_pair(x, 7, nk, dk, both_k.pages, 7 + nk * dk, nv, dv, both_v.pages, *where, st)
+    ops.rows_to_pages(x, c0, nk, dk, *where, single_k.pages, st)
+    ops.rows_to_pages(x, c0 + nk * dk, nv, dv, *where, single_v.pages, st)
+    ops.rows_to_pages_pair(x, c0, nk, dk, both_k.pages, c0 + nk * dk, nv, dv, both_v.pages, *where, st)
     assert st.tolist()[0] == 0
     assert torch.equal(single_k.pages, both_k.pages) and torch.equal(single_v.pages, both_v.pages)
     page = int(single_k.table[single_k.slots[1], 1])
-    assert torch.equal(both_v.pages[page, 1, 3], x[9 + 64 + 3, 7 + nk * dk + dv:7 + nk * dk + 2 * dv])
+    assert torch.equal(both_v.pages[page, 1, 3], x[9 + 64 + 3, c0 + nk * dk + dv:c0 + nk * dk + 2 * dv])
+    assert torch.equal(both_k.pages[page, 2, 65 - 64], x[9 + 65, c0 + 2 * dk:c0 + 3 * dk])
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("rot", [0, 6, 10])
-def test_latent_rows_and_turned_queries(ops, dtype, rot):
+@pytest.mark.parametrize("dr", [10, 16])
+def test_latent_rows_and_turned_queries(ops, dtype, rot, dr):
     """The cached row [normed low-rank part | turned shared key part] and the turned part of the queries, for tokens at
     positions around a page border, on pages handed out in shuffled order."""
-    nh, d, dr, r = 3, 8, 10, 24
+    nh, d, r = 3, 8, 24
     lens, q_lens = [70, 130], [9, 130]
     pg = Paged(lens, 1, r + dr, dtype, seed=6)
     g = torch.Generator().manual_seed(rot)
