@@ -668,6 +668,8 @@ ONE_LAYER = {
     "latent with a turned part, rows the tensor cores take": _layer(_latent(3, 16, 16, 128, 0.2, rot_dim=64, dims=64, base=300.0),
                                                                    None),
     "two maps, chunk 33, heads the tensor cores take": _layer(_diff(4, 2, 64, 64, 0.12, 0.5, size=33), None),
+    "latent, rows of 512 + 64": _layer(_latent(2, 128, 128, 512, 0.07, rot_dim=64, dims=64, base=1e4), None),
+    "two maps, chunk 100, heads of 128": _layer(_diff(4, 2, 128, 128, 0.09, 0.4, size=100), None),
     "dense": _layer(_diff(1, 1, 8, 8, 0.3, 0.5), _dense(90)),
     "one expert of seven": _layer(_latent(1, 8, 8, 8, 0.3), _moe(7, 1, 24)),
     "every expert": _layer(_latent(1, 8, 8, 8, 0.3), _moe(4, 4, 40)),
