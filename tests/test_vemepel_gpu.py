@@ -48,7 +48,9 @@ def _layer(mixer, mlp):
 # The tests' own models.  A: sizes that are no multiple of 8 or 32, groups of 3 and 1, a chunk that is no multiple of a
 # page and a reader with another chunk, a rotated part of which only some features turn, one chosen expert and all experts
 # chosen, a layer without feed-forward.  B: rounder sizes, a chunk of exactly a page, two readers of one layer's keys (one
-# without a mask), rank and head sizes that differ everywhere.
+# without a mask), rank and head sizes that differ everywhere.  C: sizes that the tensor-core attentions take in bfloat16
+# (cached rows of 128, 192 and 256 features, two maps with heads of 64 in groups of 2), a differential layer first and its
+# reader three layers on with another chunk.
 CONFIGS = {
     "A": {"architecture": "Vemepel", "vocab": 131, "width": 72, "logit_scale": 0.7, "norm": {"eps": 2e-6},
           "layers": [
@@ -64,8 +66,15 @@ CONFIGS = {
               _layer(_diff(4, 1, 32, 64, 0.15, 0.6, size=64, kv_from=1), _moe(4, 2, 96)),
               _layer(_latent(4, 32, 32, 64, 0.17), _dense(192)),
               _layer(_diff(4, 1, 32, 64, 0.2, 0.35, kv_from=1), None)]},
+    "C": {"architecture": "Vemepel", "vocab": 200, "width": 96, "logit_scale": 0.5, "norm": {"eps": 1e-5},
+          "layers": [
+              _layer(_diff(4, 2, 64, 64, 0.125, 0.55, size=96), _dense(160)),
+              _layer(_latent(3, 32, 48, 128, 0.15), _moe(6, 2, 48)),
+              _layer(_latent(2, 24, 40, 128, 0.16, rot_dim=64, dims=64, base=2000.0), None),
+              _layer(_diff(4, 2, 64, 64, 0.11, 0.3, size=40, kv_from=0), _moe(4, 1, 64)),
+              _layer(_latent(5, 16, 16, 256, 0.2), _dense(120))]},
 }
-SEEDS = {"A": 31, "B": 32}
+SEEDS = {"A": 31, "B": 32, "C": 33}
 
 
 def _tokens(vocab, n, seed):
@@ -699,7 +708,7 @@ def test_each_mechanism_alone_whole_and_token_by_token(pe, models, name, dtype):
 
 # ---- whole models -----------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
 def test_whole_prompt_and_its_first_tokens(pe, models, key, dtype):
     eng = models.engine(key, dtype)
     toks = _tokens(CONFIGS[key]["vocab"], 300, 1)
@@ -718,7 +727,7 @@ def test_whole_prompt_and_its_first_tokens(pe, models, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
 def test_long_token_by_token_decoding_equals_the_prompt(pe, models, key, dtype):
     """A short prompt, then 240 tokens one by one (over every chunk's edge, over three page borders, through CUDA
     graphs), against the plain implementation of the whole sequence."""
@@ -733,7 +742,7 @@ def test_long_token_by_token_decoding_equals_the_prompt(pe, models, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
 @pytest.mark.parametrize("portion", [2, 3, 37, 64, 65, 131])
 def test_a_prompt_fed_in_portions(pe, models, key, dtype, portion):
     eng = models.engine(key, dtype)
@@ -749,7 +758,7 @@ def test_a_prompt_fed_in_portions(pe, models, key, dtype, portion):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B"])
+@pytest.mark.parametrize("key", ["A", "B", "C"])
 def test_unequal_batches_on_slots_used_again(pe, models, key, dtype):
     """Two batches in a row on the same slots and pages: unequal prompts in one step (among them one token), then one
     token each until the shorter ones have ended; each request against itself alone in the plain implementation."""
