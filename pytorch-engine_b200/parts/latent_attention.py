@@ -29,7 +29,10 @@ from .registry import register
 from .spec import CacheRequest, WeightDecl
 
 
-LATENT_SPLIT_KEYS = 128   # keys per partial result of the tensor-core decode kernel while one wave of blocks holds them
+# Keys per partial result of the tensor-core decode kernel while one wave of blocks holds them.  Measured with 16 heads and
+# rows of 576: 8 sequences at 2,048 keys 30.8 us with 128, 32.8 with 256, 40.4 with 512; one sequence at 8,192 keys 55.9,
+# 43.1, 45.2 (a partial result is 512 floats a head, and the merge reads them all).
+LATENT_SPLIT_KEYS = 256
 
 
 def attend_rows(ops, decode, qfull, mixed, n_seqs, max_q, n_heads, row, rank, scale, seq_qstart, seq_past, seq_slot, page_table,
