@@ -4,11 +4,11 @@ sampling, and hand-written CUDA kernels.  Built-in architectures: the Qwen3 dens
 a sink and rotated values, a linear-recurrence mixer, per-layer token inputs) and Lunadra (parallel blocks of matrix-memory
 recurrences, window attention beside a gated delta rule, routed experts)."""
 from . import config, parts, cache, weights, kernels, sampling, architectures, engine
-from .config import ConfigError, LunadraConfig, Qwen3Config, VabelornConfig, VemepelConfig, load_config, preset, register_architecture
+from .config import ConfigError, LunadraConfig, Qwen3Config, VabelornConfig, VemepelConfig, ZonevikConfig, load_config, preset, register_architecture
 from .engine import Engine, GenerationResult, StepEntry, StreamChunk
 from .sampling import SamplingParams
 from .weights import WeightError, load_weights, write_random_model
 
 __all__ = ["config", "parts", "cache", "weights", "kernels", "sampling", "architectures", "engine", "ConfigError",
-           "Qwen3Config", "VabelornConfig", "LunadraConfig", "VemepelConfig", "load_config", "preset", "register_architecture", "Engine", "GenerationResult", "StepEntry",
+           "Qwen3Config", "VabelornConfig", "LunadraConfig", "VemepelConfig", "ZonevikConfig", "load_config", "preset", "register_architecture", "Engine", "GenerationResult", "StepEntry",
            "StreamChunk", "SamplingParams", "WeightError", "load_weights", "write_random_model"]

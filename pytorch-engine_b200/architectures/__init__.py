@@ -1,5 +1,5 @@
 """Architectures known to the registry.  Each module turns a typed configuration into a plan of
 parts and registers itself under the name that ``config.json`` carries in ``architectures[0]``."""
-from . import lunadra, qwen3, vabelorn, vemepel  # noqa: F401
+from . import lunadra, qwen3, vabelorn, vemepel, zonevik  # noqa: F401
 
-__all__ = ["lunadra", "qwen3", "vabelorn", "vemepel"]
+__all__ = ["lunadra", "qwen3", "vabelorn", "vemepel", "zonevik"]

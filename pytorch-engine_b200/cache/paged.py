@@ -255,7 +255,9 @@ class PagedCache:
                 first_key = max(first_key, new_length // c * c)
             first_needed = first_key // PAGE_TOKENS
             pages = g.pages_of_slot[slot]
-            for logical in range(min(first_needed, len(pages))):
+            # the pages of the first positions that a window keeps visible stay
+            kept = pages_for(g.request.keep_first) if (w and g.request.keep_first) else 0
+            for logical in range(kept, min(first_needed, len(pages))):
                 if pages[logical] >= 0:
                     g.pool.give_back(pages[logical])
                     pages[logical] = -1

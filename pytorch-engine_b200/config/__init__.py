@@ -7,9 +7,10 @@ from .qwen3 import Qwen3Config
 from .vabelorn import VabelornConfig
 from .lunadra import LunadraConfig
 from .vemepel import VemepelConfig
+from .zonevik import ZonevikConfig
 
 __all__ = [
     "ConfigError", "ModelConfig", "read_config_dict", "Architecture", "architecture", "architecture_names",
-    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig", "LunadraConfig", "VemepelConfig",
+    "architecture_of", "load_config", "register_architecture", "unregister_architecture", "Qwen3Config", "VabelornConfig", "LunadraConfig", "VemepelConfig", "ZonevikConfig",
     "preset", "preset_names", "register_preset_folder", "unregister_preset_folder",
 ]

@@ -26,7 +26,7 @@ int pe_attention_generic_ex(int dtype, int decode, const void* q, long long q_ld
     cudaStream_t stream);
 int pe_attention_generic_masked(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
     int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale, int window, int chunk,
-    int v_ld, int v_heads, int out_f32, int sink, const float* out_cos, const float* out_sin, int out_rot, int out_rows, int out_inter,
+    int keep_first, int v_ld, int v_heads, int out_f32, int sink, const float* out_cos, const float* out_sin, int out_rot, int out_rows, int out_inter,
     const int* seq_qstart, const int* seq_past, const int* seq_slot, const int* page_table, int table_stride,
     int num_pages, const void* k_pages, const void* v_pages, float* scratch, int split_keys, int max_splits, int* status,
     cudaStream_t stream);
@@ -101,6 +101,8 @@ int pe_latent_prepare(int dtype, const void* x, long long x_ld, int q_col0, int 
 // embedding.cu
 int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,
     int* status, cudaStream_t stream);
+int pe_embed_gather_scaled(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden, int vocab,
+    float scale, float* copy, int* status, cudaStream_t stream);
 
 // gemm_smallm.cu
 int pe_gemm_smallm_supported(int M, int N, int K);
@@ -146,7 +148,7 @@ int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_tokens, int n
     int rotary_dim, int table_rows, int interleaved, int v_unit_norm, const float* v_cos, const float* v_sin,
     int v_rotary_dim, int v_table_rows, int v_interleaved, const int* token_seq, const int* token_pos,
     const int* seq_slot, const int* seq_qstart, const int* page_table, int table_stride, int num_pages, void* k_pages,
-    void* v_pages, int write_cache, int* status, cudaStream_t stream);
+    void* v_pages, int write_cache, const float* bias, int* status, cudaStream_t stream);
 
 // sampling.cu
 long long pe_sample_scratch_bytes(int n_rows, int vocab, float temperature, int top_k, float top_p, float min_p);
@@ -189,19 +191,21 @@ int pe_mlstm_recurrence(int dtype, const void* q, const void* k, const void* v, 
 long long pe_mlstm_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks);
 
 // delta_rule.cu
-int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, int taps, float* tail,
+int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, const float* bias, int taps, float* tail,
     const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out, int n_tokens, int n_seqs, int channels,
     int n_slots, int* status, cudaStream_t stream);
 int pe_delta_rule_recurrence(int dtype, const void* qkv, const float* a, const float* dt_bias, const float* A_log,
     const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps, float q_scale, void* out, float* S,
     const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots,
-    int chunk, int max_chunks, float* scratch, int* status, cudaStream_t stream);
+    int chunk, int max_chunks, float* scratch, int head_decay, int gate_silu, int* status, cudaStream_t stream);
 long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks);
 
 // moe.cu
 int pe_moe_route(const float* logits, const float* correction, int n_tokens, int n_all, int top, int* chosen,
     float* weight, int* dense_rows, int n_real, cudaStream_t stream);
 int pe_moe_route_logits(const float* logits, const float* bias, int n_tokens, int n_all, int top, int* chosen,
+    float* weight, int* dense_rows, int n_real, cudaStream_t stream);
+int pe_moe_route_sigmoid_groups(const float* logits, int n_tokens, int n_all, int top, int n_groups, int keep, int* chosen,
     float* weight, int* dense_rows, int n_real, cudaStream_t stream);
 int pe_moe_group(const int* chosen, int n_tokens, int top, int n_real, int* offsets, int* row_token, int* pair_row,
     cudaStream_t stream);
@@ -214,6 +218,23 @@ int pe_moe_combine(int dtype, const void* rows, const void* x, const void* share
     const float* weight, int top, void* out, int n_tokens, int width, cudaStream_t stream);
 int pe_glu_act(int dtype, const void* gate_up, void* out, int n_rows, int inter, int kind, float limit, float alpha,
     cudaStream_t stream);
+
+// ssd.cu
+int pe_ssd_recurrence(int dtype, const void* xbc, long long xbc_ld, const void* dt, long long dt_ld, const float* dt_bias,
+    const float* A_log, const float* D, float* y, float* S, const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q,
+    int heads, int groups, int n, int dv, int n_slots, int chunk, int max_chunks, float* scratch, int* status,
+    cudaStream_t stream);
+long long pe_ssd_scratch_floats(int n_seqs, int heads, int n, int dv, int max_chunks);
+int pe_gated_part_norm(int dtype, const float* y, const void* z, long long z_ld, const float* w, float eps, void* out,
+    int n_tokens, int width, int parts, cudaStream_t stream);
+
+// dyt.cu
+int pe_dyt(int dtype, int in_f32, const void* x, const int* rows, const float* w, const float* b, float alpha, void* out,
+    int n_rows, int dim, cudaStream_t stream);
+int pe_dyt_add(int dtype, float* stream_rows, const void* delta, const float* w1, const float* b1, float alpha1,
+    const float* w2, const float* b2, float alpha2, void* out, int n_rows, int dim, cudaStream_t stream);
+int pe_rmsnorm_pair_mix(int dtype, const void* a, const void* b, const float* wa, const float* wb, float eps, float sa,
+    float sb, void* out, int n_rows, int dim, cudaStream_t stream);
 
 // wait_probe.cu
 int pe_wait_probe(unsigned long long* out, int polls, cudaStream_t stream);

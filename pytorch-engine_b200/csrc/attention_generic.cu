@@ -52,6 +52,7 @@ struct AttnArgs {
   int v_heads;                        // value heads in a page; kv head g reads value head g % v_heads (several key
                                       //   maps over one set of values)
   int out_f32;                        // != 0: `out` is float32 whatever the inputs' type (not with a turned output)
+  int keep_first;                     // > 0: with a window, keys at positions < keep_first stay visible to every later query
 };
 
 // First visible key of a query at `qpos` under the window and chunk masks.
@@ -198,14 +199,16 @@ __global__ void __launch_bounds__(256) attn_prefill_kernel(AttnArgs a) {
   const int k_begin = first_visible(a, past + first) / kTileKeys * kTileKeys;   // of the block's first query
   const int k_end = last_pos + 1;
   const int my_lo = first_visible(a, qpos);
-  for (int k0 = k_begin; k0 < k_end; k0 += kTileKeys) {
+  const int keep = a.keep_first > 0 ? min(a.keep_first, k_begin) : 0;             // kept keys in front of the window
+  for (int k0 = keep > 0 ? 0 : k_begin; k0 < k_end; k0 += kTileKeys) {
+    if (k0 >= keep && k0 < k_begin) k0 = k_begin;   // between the kept keys and the window nobody sees anything
     __syncthreads();  // everyone is done with the previous tile (and q is written, first time)
     load_tile<T>(a, slot, kvh, k0, k_end, Ks, Vs, threadIdx.x, blockDim.x);
     __syncthreads();
     if (!active || k0 > qpos) continue;  // the whole tile lies in this query's future
     const int kpos = k0 + lane;
-    const bool visible = kpos <= qpos && kpos >= my_lo;
-    if (k0 + kTileKeys - 1 < my_lo) continue;  // the whole tile lies before what this query sees
+    const bool visible = kpos <= qpos && (kpos >= my_lo || kpos < a.keep_first);
+    if (k0 + kTileKeys - 1 < my_lo && k0 >= a.keep_first) continue;  // the whole tile lies before what this query sees
     fold_tile<DPL>(qs, Ks, Vs, d, dv, n_here, a.scale, visible, lane, m, l, acc);
   }
   if (!active) return;
@@ -270,7 +273,8 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
   int k_lo = split * a.split_keys, k_hi = min(len, k_lo + a.split_keys);
   if (k_lo >= len) return;
   const int win_lo = first_visible(a, qpos);
-  if (k_hi <= win_lo) return;                    // the whole range lies before the window or the chunk
+  const int keep = a.keep_first > 0 ? min(a.keep_first, win_lo) : 0;   // kept keys in front of the window
+  if (k_hi <= win_lo && k_lo >= keep) return;    // the whole range lies before the window or the chunk
   const int slot = a.seq_slot[b];
   for (int i = threadIdx.x; i < kGT * d; i += blockDim.x) {
     const int h = i / d, c = i - h * d;
@@ -285,14 +289,15 @@ __global__ void __launch_bounds__(NW * 32) attn_decode_split_kernel(AttnArgs a) 
 #pragma unroll
     for (int i = 0; i < DPL; ++i) acc[h][i] = 0.f;
   }
-  const int first_tile = max(k_lo, win_lo) / kTileKeys;
+  const int first_tile = (k_lo < keep ? k_lo : max(k_lo, win_lo)) / kTileKeys;
   const int last_tile = (k_hi - 1) / kTileKeys;
   for (int tile = first_tile + warp; tile <= last_tile; tile += NW) {
     const int k0 = tile * kTileKeys;
+    if (k0 >= keep && k0 + kTileKeys <= win_lo) continue;   // between the kept keys and the window
     load_tile<T>(a, slot, kvh, k0, k_hi, Ks, Vs, lane, 32);
     __syncwarp();
     const int kpos = k0 + lane;
-    const bool visible = kpos >= max(k_lo, win_lo) && kpos < k_hi;
+    const bool visible = kpos >= k_lo && (kpos >= win_lo || kpos < keep) && kpos < k_hi;
     fold_tile<DPL>(Qs, Ks, Vs, d, dv, n_here, a.scale, visible, lane, m, l, acc);
     __syncwarp();
   }
@@ -350,11 +355,18 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
   }
   const int win_lo = first_visible(a, len - 1);
   const int first = min(win_lo / a.split_keys, n_splits);
+  // ranges in front of the window that hold kept keys were computed too: [0, kept_ranges)
+  const int keep = a.keep_first > 0 ? min(a.keep_first, win_lo) : 0;
+  const int kept_ranges = min((keep + a.split_keys - 1) / a.split_keys, first);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   float mx = a.sink ? 0.f : -INFINITY;   // the sink is one more range whose log-sum is 0 and whose output is 0
-  for (int s = first; s < n_splits; ++s) mx = fmaxf(mx, a.part_lse[base + s]);
+  for (int s = 0; s < n_splits; ++s) {
+    if (s >= kept_ranges && s < first) continue;
+    mx = fmaxf(mx, a.part_lse[base + s]);
+  }
   float denom = a.sink ? expf(-mx) : 0.f;
-  for (int s = first; s < n_splits; ++s) {
+  for (int s = 0; s < n_splits; ++s) {
+    if (s >= kept_ranges && s < first) continue;
     const float e = a.part_lse[base + s];
     denom += (e == -INFINITY) ? 0.f : expf(e - mx);
   }
@@ -362,7 +374,8 @@ __global__ void attn_decode_combine_kernel(AttnArgs a) {
   T* o = (T*)a.out + (size_t)t * a.out_ld + (size_t)h * d;
   for (int c = threadIdx.x; c < d; c += blockDim.x) {
     float v = 0.f;
-    for (int s = first; s < n_splits; ++s) {
+    for (int s = 0; s < n_splits; ++s) {
+      if (s >= kept_ranges && s < first) continue;
       const float e = a.part_lse[base + s];
       const float w = (e == -INFINITY) ? 0.f : expf(e - mx) * inv;
       v = fmaf(w, a.part_acc[(base + s) * d + c], v);
@@ -474,17 +487,19 @@ extern "C" int pe_attention_generic_ex(int dtype, int decode, const void* q, lon
                                        int num_pages, const void* k_pages, const void* v_pages, float* scratch,
                                        int split_keys, int max_splits, int* status, cudaStream_t stream) {
   return pe_attention_generic_masked(dtype, decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim,
-                                     v_dim, scale, window, 0, v_dim, n_kv_heads, 0, sink, out_cos, out_sin, out_rot, out_rows,
+                                     v_dim, scale, window, 0, 0, v_dim, n_kv_heads, 0, sink, out_cos, out_sin, out_rot, out_rows,
                                      out_inter, seq_qstart, seq_past, seq_slot, page_table, table_stride, num_pages,
                                      k_pages, v_pages, scratch, split_keys, max_splits, status, stream);
 }
 
-// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), value rows
+// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), kept first keys
+// (`keep_first` > 0 with a window: positions below it stay visible however far back they lie), value rows
 // `v_ld` elements apart (>= v_dim), `v_heads` value heads a page (kv head g reads value head g % v_heads), and
 // optionally a float32 output (`out_f32`: out_ld then counts floats).
 extern "C" int pe_attention_generic_masked(int dtype, int decode, const void* q, long long q_ld, void* out, long long out_ld,
                                            int n_seqs, int max_q, int n_heads, int n_kv_heads, int head_dim, int v_dim,
-                                           float scale, int window, int chunk, int v_ld, int v_heads, int out_f32, int sink,
+                                           float scale, int window, int chunk, int keep_first, int v_ld, int v_heads, int out_f32,
+                                           int sink,
                                            const float* out_cos, const float* out_sin, int out_rot, int out_rows,
                                            int out_inter, const int* seq_qstart, const int* seq_past, const int* seq_slot,
                                            const int* page_table, int table_stride, int num_pages, const void* k_pages,
@@ -494,7 +509,9 @@ extern "C" int pe_attention_generic_masked(int dtype, int decode, const void* q,
   if (n_heads <= 0 || n_kv_heads <= 0 || head_dim <= 0 || v_dim <= 0 || n_heads % n_kv_heads) return PE_ERR_BAD_ARGUMENT;
   if (out_cos && (!out_sin || out_rot <= 0 || out_rot > v_dim || (out_rot & 1))) return PE_ERR_BAD_ARGUMENT;
   if (v_ld < v_dim || v_heads <= 0 || chunk < 0 || (out_f32 && out_cos)) return PE_ERR_BAD_ARGUMENT;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return PE_ERR_BAD_ARGUMENT;
   pe::AttnArgs a;
+  a.keep_first = window > 0 ? keep_first : 0;
   a.chunk = chunk; a.v_ld = v_ld; a.v_heads = v_heads; a.out_f32 = out_f32;
   a.v_dim = v_dim; a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin;
   a.out_rot = out_cos ? out_rot : 0; a.out_rows = out_rows; a.out_inter = out_inter;
@@ -571,7 +588,7 @@ extern "C" int pe_attention_decode_noalloc(int dtype, const void* q, long long q
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
   a.k_pages = k_pages; a.v_pages = v_pages; a.status = status;
   a.split_keys = split_keys; a.max_splits = max_splits;
-  a.chunk = 0; a.v_ld = head_dim; a.v_heads = n_kv_heads; a.out_f32 = 0;
+  a.chunk = 0; a.v_ld = head_dim; a.v_heads = n_kv_heads; a.out_f32 = 0; a.keep_first = 0;
   a.v_dim = head_dim; a.sink = 0; a.out_cos = nullptr; a.out_sin = nullptr; a.out_rot = 0; a.out_rows = 0; a.out_inter = 0;
   a.part_acc = scratch;
   a.part_lse = scratch + (size_t)n_seqs * n_heads * max_splits * head_dim;

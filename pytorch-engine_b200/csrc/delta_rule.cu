@@ -4,9 +4,9 @@
 //   convolution  y[t][c] = silu(sum_j w[c][j] x[t - taps + 1 + j][c])       inputs before a sequence's start are zero,
 //                                                                           before this step's start they come from the state
 //   unit vectors q = q / sqrt(sum q^2 + 1e-6) * q_scale ;  k = k / sqrt(sum k^2 + 1e-6)          per head
-//   decay        g[i] = exp(-exp(A) softplus(a[i] + dt[i]))                 per head and key channel
+//   decay        g[i] = exp(-exp(A) softplus(a[i] + dt[i]))                 per head and key channel, or one per head
 //   step         S <- diag(g) S ;  u = beta (v - S^T k) ;  S <- S + k u^T ;  o = S^T q            beta = sigmoid(b)
-//   out          = o / rms(o) * w * sigmoid(gate)                           per head, eps inside the root, w of size dv
+//   out          = o / rms(o) * w * sigmoid(gate)  (or * silu(gate))        per head, eps inside the root, w of size dv
 //
 // A block owns one head's S [d, dv] of one sequence (in registers or in shared memory) and walks the sequence's tokens
 // of this step in order; thread j owns column j.  State, decay, beta, the unit vectors and the head norm are float32 whatever
@@ -20,7 +20,7 @@ namespace pe {
 // x: [n_tokens, ld] (channels at columns col0 .. col0 + channels), w: [channels, taps] float32,
 // tail: [slots, taps - 1, channels] float32 (the last inputs of every sequence, oldest first).
 template <typename T>
-__global__ void short_conv_kernel(const T* x, long long ld, int col0, const float* __restrict__ w, int taps,
+__global__ void short_conv_kernel(const T* x, long long ld, int col0, const float* __restrict__ w, const float* __restrict__ bias, int taps,
                                   const float* tail, const int* token_seq, const int* seq_slot, const int* seq_qstart,
                                   T* __restrict__ out, int n_tokens, int channels, int n_slots, int* status) {
   pdl_wait_block();
@@ -35,7 +35,7 @@ __global__ void short_conv_kernel(const T* x, long long ld, int col0, const floa
     return;
   }
   for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    float acc = 0.f;
+    float acc = bias ? bias[c] : 0.f;
     for (int j = 0; j < taps; ++j) {
       const int src = t - (taps - 1) + j;          // row of the step, if it belongs to this sequence
       float v;
@@ -53,14 +53,14 @@ __global__ void short_conv_kernel(const T* x, long long ld, int col0, const floa
 
 template <int TAPS>
 __global__ void short_conv_vec8_kernel(const __nv_bfloat16* x, long long ld, int col0, const float* __restrict__ w,
-                                       const float* tail, const int* token_seq, const int* seq_slot, const int* seq_qstart,
+                                       const float* __restrict__ bias, const float* tail, const int* token_seq, const int* seq_slot, const int* seq_qstart,
                                        __nv_bfloat16* __restrict__ out, int n_tokens, int channels, int n_slots, int* status,
                                        int kConvStrip) {
   const int per_row = channels / 8;
   const int strips = (n_tokens + kConvStrip - 1) / kConvStrip;
   const size_t total = (size_t)strips * per_row;
   const size_t idx0 = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-  float wr[8][TAPS];
+  float wr[8][TAPS], br[8];
   int c_have = -1;
   pdl_wait_block();
   pdl_launch_dependents();
@@ -71,6 +71,8 @@ __global__ void short_conv_vec8_kernel(const __nv_bfloat16* x, long long ld, int
       for (int e = 0; e < 8; ++e)
 #pragma unroll
         for (int j = 0; j < TAPS; ++j) wr[e][j] = w[(size_t)(c + e) * TAPS + j];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) br[e] = bias ? bias[c + e] : 0.f;
       c_have = c;
     }
     const int t_end = min(n_tokens, (strip + 1) * kConvStrip);
@@ -84,7 +86,7 @@ __global__ void short_conv_vec8_kernel(const __nv_bfloat16* x, long long ld, int
       }
       float acc[8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+      for (int e = 0; e < 8; ++e) acc[e] = br[e];
 #pragma unroll
       for (int j = 0; j < TAPS; ++j) {
         const int src = t - (TAPS - 1) + j;
@@ -139,8 +141,8 @@ __global__ void conv_tail_kernel(const T* x, long long ld, int col0, float* tail
 // ---- the recurrence -----------------------------------------------------------------------------------------------
 struct DeltaArgs {
   const void* qkv;          // [n_tokens, channels] after the convolution: q (kv_heads * d) | k (kv_heads * d) | v (heads * dv)
-  const float* a;           // [n_tokens, heads * d]: the decay projection before its offset
-  const float* dt_bias;     // [heads * d]
+  const float* a;           // [n_tokens, heads * d]: the decay projection before its offset ([n_tokens, heads] with head_decay)
+  const float* dt_bias;     // [heads * d] ([heads] with head_decay)
   const float* A_log;       // [heads]
   const float* b;           // [n_tokens, heads]: beta before the sigmoid
   const void* gate; long long gate_ld;   // [n_tokens, heads * dv] in the run dtype, before the sigmoid
@@ -154,6 +156,8 @@ struct DeltaArgs {
   int max_chunks;
   float* scratch;           // [n_seqs, max_chunks, heads, d * dv + d * d]: a chunk's S, then its transition matrix
   int* status;
+  int head_decay;           // != 0: one decay per head and token instead of one per key channel
+  int gate_silu;            // != 0: the output gate is silu(gate) instead of sigmoid(gate)
 };
 
 __host__ __device__ inline size_t delta_unit(int d, int dv) { return (size_t)d * dv + (size_t)d * d; }
@@ -267,7 +271,8 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
     // the decays: exp(-exp(A) softplus(a + dt)) per token and key channel
     for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
       const int tt = e / d, i = e - tt * d;
-      const float z = a.a[(size_t)(tb + tt) * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
+      const float z = a.head_decay ? a.a[(size_t)(tb + tt) * a.heads + head] + a.dt_bias[head]
+                                   : a.a[(size_t)(tb + tt) * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
       const float softplus = z > 20.f ? z : log1pf(expf(z));
       db[(size_t)tt * dpad + i] = expf(-rate * softplus);
     }
@@ -387,7 +392,7 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
       const float ss = block_sum((i0 == 0 && j < dv) ? o * o : 0.f, red);
       if (j < dv && i0 == 0) {
         const float gate = to_f32<T>(gb[(size_t)tt * dv + j]);
-        const float y = o * rsqrtf(ss / (float)dv + a.eps) * nw / (1.f + expf(-gate));
+        const float y = o * rsqrtf(ss / (float)dv + a.eps) * nw * (a.gate_silu ? gate : 1.f) / (1.f + expf(-gate));
         ((T*)a.out)[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = from_f32<T>(y);
       }
     }
@@ -530,7 +535,7 @@ static int delta_run(const DeltaArgs& a, cudaStream_t stream) {
 
 }  // namespace pe
 
-extern "C" int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, int taps, float* tail,
+extern "C" int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const float* w, const float* bias, int taps, float* tail,
                                   const int* token_seq, const int* seq_slot, const int* seq_qstart, void* out,
                                   int n_tokens, int n_seqs, int channels, int n_slots, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
@@ -538,20 +543,20 @@ extern "C" int pe_short_conv_silu(int dtype, const void* x, long long ld, int co
   const int threads = channels >= 1024 ? 256 : 128;
   if (dtype != PE_F32 && dtype != PE_BF16) return PE_ERR_UNSUPPORTED_DTYPE;
   const bool vec8 = dtype == PE_BF16 && taps >= 2 && taps <= 4 && channels % 8 == 0 && ld % 8 == 0 && col0 % 8 == 0 &&
-                    (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)tail % 16 == 0;
+                    (uintptr_t)x % 16 == 0 && (uintptr_t)out % 16 == 0 && (uintptr_t)tail % 16 == 0;   // (taps == 1: no tail is read)
   if (vec8) {
     const int strip = n_tokens >= 512 ? 8 : 1;
     const size_t total = (size_t)((n_tokens + strip - 1) / strip) * (channels / 8);
     size_t blocks = (total + 127) / 128;
     if (blocks > (size_t)pe::kSMs * 32) blocks = (size_t)pe::kSMs * 32;
     auto kernel = taps == 2 ? pe::short_conv_vec8_kernel<2> : (taps == 3 ? pe::short_conv_vec8_kernel<3> : pe::short_conv_vec8_kernel<4>);
-    pe::launch(kernel, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)x, ld, col0, w, (const float*)tail, token_seq, seq_slot,
+    pe::launch(kernel, (int)blocks, 128, 0, stream, (const __nv_bfloat16*)x, ld, col0, w, bias, (const float*)tail, token_seq, seq_slot,
                seq_qstart, (__nv_bfloat16*)out, n_tokens, channels, n_slots, status, strip);
   } else if (dtype == PE_F32)
-    pe::launch(pe::short_conv_kernel<float>, n_tokens, threads, 0, stream, (const float*)x, ld, col0, w, taps, (const float*)tail,
+    pe::launch(pe::short_conv_kernel<float>, n_tokens, threads, 0, stream, (const float*)x, ld, col0, w, bias, taps, (const float*)tail,
                token_seq, seq_slot, seq_qstart, (float*)out, n_tokens, channels, n_slots, status);
   else
-    pe::launch(pe::short_conv_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)x, ld, col0, w, taps,
+    pe::launch(pe::short_conv_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)x, ld, col0, w, bias, taps,
                (const float*)tail, token_seq, seq_slot, seq_qstart, (__nv_bfloat16*)out, n_tokens, channels, n_slots, status);
   PE_LAUNCH_CHECK();
   if (taps > 1) {
@@ -578,13 +583,14 @@ extern "C" int pe_delta_rule_recurrence(int dtype, const void* qkv, const float*
                                         const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps,
                                         float q_scale, void* out, float* S, const int* seq_slot, const int* seq_qstart,
                                         int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots, int chunk,
-                                        int max_chunks, float* scratch, int* status, cudaStream_t stream) {
+                                        int max_chunks, float* scratch, int head_decay, int gate_silu, int* status,
+                                        cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || d <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
   if (dv > 1024 || d > 1024) return PE_ERR_UNSUPPORTED_SIZE;
   if (dtype != PE_F32 && dtype != PE_BF16) return PE_ERR_UNSUPPORTED_DTYPE;
   pe::DeltaArgs args{qkv, a, dt_bias, A_log, b, gate, gate_ld, norm_w, eps, q_scale, out, S, seq_slot, seq_qstart,
-                     n_seqs, heads, kv_heads, d, dv, n_slots, 0, 1, nullptr, status};
+                     n_seqs, heads, kv_heads, d, dv, n_slots, 0, 1, nullptr, status, head_decay, gate_silu};
   if (chunk > 0) {
     if (!scratch || max_chunks <= 0 || (long long)max_chunks * chunk < max_q || max_chunks > 32767) return PE_ERR_BAD_ARGUMENT;
     args.chunk = chunk; args.max_chunks = max_chunks; args.scratch = scratch;

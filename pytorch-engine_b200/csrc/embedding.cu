@@ -7,7 +7,8 @@ namespace pe {
 
 template <typename T>
 __global__ void embed_gather_kernel(const T* __restrict__ table, const int* ids,
-                                    float* __restrict__ out, int n_tokens, int hidden, int vocab, int* status) {
+                                    float* __restrict__ out, int n_tokens, int hidden, int vocab, int* status, float scale,
+                                    float* __restrict__ copy) {
   pdl_wait_block();
   pdl_launch_dependents();
   const int row = blockIdx.x;
@@ -16,12 +17,19 @@ __global__ void embed_gather_kernel(const T* __restrict__ table, const int* ids,
   if (id < 0 || id >= vocab) {
     if (threadIdx.x == 0) report(status, kStatusTokenOutOfRange, row, id, vocab);
     // the row is still defined: zeros
-    for (int c = threadIdx.x; c < hidden; c += blockDim.x) out[(size_t)row * hidden + c] = 0.f;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+      out[(size_t)row * hidden + c] = 0.f;
+      if (copy) copy[(size_t)row * hidden + c] = 0.f;
+    }
     return;
   }
   const T* src = table + (size_t)id * hidden;
   float* dst = out + (size_t)row * hidden;
-  for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = to_f32<T>(src[c]);
+  for (int c = threadIdx.x; c < hidden; c += blockDim.x) {
+    const float v = to_f32<T>(src[c]) * scale;
+    dst[c] = v;
+    if (copy) copy[(size_t)row * hidden + c] = v;
+  }
 }
 
 // Token embedding plus an embedding of the pair (previous token, token):
@@ -73,13 +81,20 @@ __global__ void embed_pair_kernel(const T* __restrict__ table, const T* __restri
 
 extern "C" int pe_embed_gather(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden,
                                int vocab, int* status, cudaStream_t stream) {
+  return pe_embed_gather_scaled(dtype, table, ids, out, n_tokens, hidden, vocab, 1.f, nullptr, status, stream);
+}
+
+// The same with a factor on every row, and optionally a second copy of the rows (what a later part reads again after the
+// first has become the residual stream).
+extern "C" int pe_embed_gather_scaled(int dtype, const void* table, const int* ids, float* out, int n_tokens, int hidden,
+                                      int vocab, float scale, float* copy, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (hidden <= 0 || vocab <= 0) return PE_ERR_BAD_ARGUMENT;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (dtype == PE_F32)
-    pe::launch(pe::embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, n_tokens, hidden, vocab, status);
+    pe::launch(pe::embed_gather_kernel<float>, n_tokens, threads, 0, stream, (const float*)table, ids, out, n_tokens, hidden, vocab, status, scale, copy);
   else if (dtype == PE_BF16)
-    pe::launch(pe::embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, status);
+    pe::launch(pe::embed_gather_kernel<__nv_bfloat16>, n_tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, n_tokens, hidden, vocab, status, scale, copy);
   else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();

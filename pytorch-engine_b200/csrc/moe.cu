@@ -4,6 +4,7 @@
 //   route     s = softmax(z) over all router outputs; the `top` largest of s + correction are chosen (ties: the
 //             lower index), each weighted with its own s (not renormalised); all in float32
 //   route by logits   the `top` largest of z + bias are chosen, weighted by a softmax over the chosen ones alone
+//   route by groups   s = sigmoid(z); only the best groups of neighbouring experts may be chosen from; weights s
 //   group     pairs whose choice is a real expert (index < n_real) are ordered by expert: offsets[e] .. offsets[e+1]
 //             are expert e's rows, row_token[r] the token of row r, pair_row[t, j] the row of a pair (-1: the
 //             choice is an identity expert, which returns its input)
@@ -100,6 +101,75 @@ __global__ void moe_route_logits_kernel(const float* logits, const float* __rest
   if (lane == 0) {
     const float inv = 1.f / sum;
     for (int j = 0; j < top; ++j) weight[(size_t)t * top + j] *= inv;
+  }
+}
+
+// The choice among groups of neighbours: s = sigmoid(z); the outputs form `n_groups` equal groups, a group's score is the sum
+// of its two largest s (its one s for groups of one), only the `keep` best groups (ties: the lower group) may be chosen from;
+// the `top` largest s among those (ties: the lower index), weighted with s itself.  n_groups <= 1: no groups.  One warp per token.
+__global__ void moe_route_sigmoid_groups_kernel(const float* logits, int n_tokens, int n_all, int top, int n_groups, int keep,
+                                                int* __restrict__ chosen, float* __restrict__ weight, int* __restrict__ dense_rows,
+                                                int n_real) {
+  extern __shared__ float gs_all[];    // [warps][n_groups]: group scores, -inf once a group is kept... then 1 / 0 flags
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+  if (t >= n_tokens) return;
+  const float* z = logits + (size_t)t * n_all;
+  float* gs = gs_all + (size_t)warp * (n_groups > 0 ? n_groups : 1);
+  const int per = n_groups > 1 ? n_all / n_groups : n_all;
+  if (n_groups > 1) {
+    for (int g = lane; g < n_groups; g += 32) {
+      float a = -INFINITY, b = -INFINITY;   // the two largest
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float sc = 1.f / (1.f + expf(-z[e]));
+        if (sc > a) { b = a; a = sc; } else if (sc > b) { b = sc; }
+      }
+      gs[g] = per > 1 ? a + b : a;
+    }
+    __syncwarp();
+    // pick the `keep` best groups one at a time; a picked group's entry becomes +inf (allowed), at the end the others -inf
+    for (int j = 0; j < keep; ++j) {
+      float best = -INFINITY;
+      int best_g = 0x7fffffff;
+      for (int g = lane; g < n_groups; g += 32) {
+        const float v = gs[g];
+        if (v != INFINITY && (v > best || best_g == 0x7fffffff)) { best = v; best_g = g; }
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1) {
+        const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+        const int og = __shfl_xor_sync(0xffffffffu, best_g, o);
+        if (og != 0x7fffffff && (best_g == 0x7fffffff || ob > best || (ob == best && og < best_g))) { best = ob; best_g = og; }
+      }
+      if (lane == 0 && best_g != 0x7fffffff) gs[best_g] = INFINITY;
+      __syncwarp();
+    }
+  }
+  unsigned long long taken_lo = 0ull;   // this lane's entries e = lane + 32 * i, bit i set once chosen (n_all <= 2048)
+  for (int j = 0; j < top; ++j) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane, i = 0; e < n_all; e += 32, ++i) {
+      if ((taken_lo >> i) & 1ull) continue;
+      if (n_groups > 1 && gs[e / per] != INFINITY) continue;
+      const float c = 1.f / (1.f + expf(-z[e]));
+      if (c > best || best_e == 0x7fffffff) { best = c; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+      const int oe = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (oe != 0x7fffffff && (best_e == 0x7fffffff || ob > best || (ob == best && oe < best_e))) { best = ob; best_e = oe; }
+    }
+    if (best_e != 0x7fffffff && (best_e & 31) == lane) taken_lo |= 1ull << (best_e >> 5);
+    if (lane == 0) {
+      const bool any = best_e != 0x7fffffff;
+      chosen[(size_t)t * top + j] = any ? best_e : -1;
+      weight[(size_t)t * top + j] = any ? best : 0.f;
+      if (dense_rows) dense_rows[(size_t)t * top + j] = (any && best_e < n_real) ? t * n_real + best_e : -1;
+    }
   }
 }
 
@@ -390,6 +460,20 @@ extern "C" int pe_moe_route_logits(const float* logits, const float* bias, int n
   const int warps = 4;
   pe::launch(pe::moe_route_logits_kernel, (n_tokens + warps - 1) / warps, warps * 32, 0, stream, logits, bias, n_tokens, n_all,
              top, chosen, weight, dense_rows, n_real);
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+extern "C" int pe_moe_route_sigmoid_groups(const float* logits, int n_tokens, int n_all, int top, int n_groups, int keep,
+                                           int* chosen, float* weight, int* dense_rows, int n_real, cudaStream_t stream) {
+  if (n_tokens <= 0) return PE_OK;
+  if (n_all <= 0 || top <= 0 || top > n_all) return PE_ERR_BAD_ARGUMENT;
+  if (n_groups > 1 && (n_all % n_groups || keep <= 0 || keep > n_groups || top > keep * (n_all / n_groups))) return PE_ERR_BAD_ARGUMENT;
+  if (n_all > 2048) return PE_ERR_UNSUPPORTED_SIZE;
+  const int warps = 4;
+  const size_t smem = (size_t)warps * (n_groups > 0 ? n_groups : 1) * sizeof(float);
+  pe::launch(pe::moe_route_sigmoid_groups_kernel, (n_tokens + warps - 1) / warps, warps * 32, smem, stream, logits, n_tokens, n_all,
+             top, n_groups, keep, chosen, weight, dense_rows, n_real);
   PE_LAUNCH_CHECK();
   return PE_OK;
 }

@@ -387,6 +387,7 @@ struct QkvRotateArgs {
   void* k_pages; void* v_pages;   // [num_pages, n_kv_heads, 64, head_dim] and [.., v_dim]
   int write_cache;
   int* status;
+  const float* bias;   // [q | k | v features] added to the projected rows first (null: none)
 };
 
 template <typename T>
@@ -439,11 +440,12 @@ __global__ void qkv_rotate_append_kernel(QkvRotateArgs a) {
   }
   const float* w = is_q ? a.q_norm_w : (is_k ? a.k_norm_w : nullptr);
   const bool normed = is_v ? (a.v_unit_norm != 0) : (w != nullptr);
+  const float* bias = a.bias ? a.bias + row_off : nullptr;
   float inv = 1.f;
   if (normed) {
     float ss = 0.f;
     for (int c = lane; c < D; c += 32) {
-      const float x = to_f32<T>(row[c]);
+      const float x = to_f32<T>(row[c]) + (bias ? bias[c] : 0.f);
       ss += x * x;
     }
     inv = rsqrtf(warp_sum(ss) / (float)D + a.eps);
@@ -460,6 +462,7 @@ __global__ void qkv_rotate_append_kernel(QkvRotateArgs a) {
   }
   auto value = [&](int c) -> float {
     float x = to_f32<T>(row[c]);
+    if (bias) x += bias[c];
     if (normed) x *= inv;
     if (w) x *= w[c];
     return x;
@@ -677,7 +680,7 @@ extern "C" int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_to
                                     int v_rotary_dim, int v_table_rows, int v_interleaved, const int* token_seq,
                                     const int* token_pos, const int* seq_slot, const int* seq_qstart,
                                     const int* page_table, int table_stride, int num_pages, void* k_pages,
-                                    void* v_pages, int write_cache, int* status, cudaStream_t stream) {
+                                    void* v_pages, int write_cache, const float* bias, int* status, cudaStream_t stream) {
   if (n_tokens <= 0) return PE_OK;
   if (head_dim <= 0 || v_dim <= 0 || n_heads <= 0 || n_kv_heads < 0) return PE_ERR_BAD_ARGUMENT;
   if (rotary_dim < 0 || rotary_dim > head_dim || (rotary_dim & 1)) return PE_ERR_UNSUPPORTED_SIZE;
@@ -692,12 +695,12 @@ extern "C" int pe_qkv_rotate_append(int dtype, void* qkv, long long ld, int n_to
   a.v_interleaved = v_interleaved;
   a.token_seq = token_seq; a.token_pos = token_pos; a.seq_slot = seq_slot; a.seq_qstart = seq_qstart;
   a.page_table = page_table; a.table_stride = table_stride; a.num_pages = num_pages;
-  a.k_pages = k_pages; a.v_pages = v_pages; a.write_cache = write_cache; a.status = status;
+  a.k_pages = k_pages; a.v_pages = v_pages; a.write_cache = write_cache; a.status = status; a.bias = bias;
   const int warps = 4;
   dim3 grid(n_tokens, (n_heads + 2 * n_kv_heads + warps - 1) / warps);
   if (grid.y > 65535) return PE_ERR_UNSUPPORTED_SIZE;
   auto al16 = [](const void* p) { return (uintptr_t)p % 16 == 0; };
-  const bool vec8 = dtype == PE_BF16 && head_dim == v_dim && head_dim % 8 == 0 && head_dim <= 256 && ld % 8 == 0 &&
+  const bool vec8 = dtype == PE_BF16 && bias == nullptr && head_dim == v_dim && head_dim % 8 == 0 && head_dim <= 256 && ld % 8 == 0 &&
                     (a.rotary_dim == 0 || (interleaved && a.rotary_dim % 8 == 0)) &&
                     (a.v_rotary_dim == 0 || (v_interleaved && a.v_rotary_dim % 8 == 0)) && al16(qkv) && al16(k_pages) &&
                     al16(v_pages) && al16(cos_table) && al16(sin_table) && al16(v_cos) && al16(v_sin) && al16(q_norm_w) &&

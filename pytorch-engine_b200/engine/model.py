@@ -102,10 +102,17 @@ class DecoderModel:
         """Run the step described by ``ctx``; returns float32 logits ``[n_want, vocab]``."""
         rt = self.runtime
         stream = ctx.buffer("model.stream", (ctx.n_tokens, self.hidden), torch.float32)
+        ctx.embedding_output = None
         if hasattr(self.embedding, "cache_request"):
             self.embedding.forward(ctx.tokens, stream, ctx, cache.view(self.EMBEDDING_KEY))
+        elif self.plan.keep_embedding_output and getattr(self.embedding, "writes_copy", False):
+            ctx.embedding_output = ctx.buffer("model.embedding_output", (ctx.n_tokens, self.hidden), torch.float32)
+            self.embedding.forward(ctx.tokens, stream, copy=ctx.embedding_output)
         else:
             self.embedding.forward(ctx.tokens, stream)
+        if self.plan.keep_embedding_output and ctx.embedding_output is None:
+            ctx.embedding_output = ctx.buffer("model.embedding_output", (ctx.n_tokens, self.hidden), torch.float32)
+            ctx.embedding_output.copy_(stream)
         ctx.stream_copy = None    # a copy of the stream in the run dtype, if a block has left one (post-norm blocks do)
         pending = None
         for run in self.plan.order:

@@ -68,7 +68,7 @@ _SIGNATURES = {
     "pe_tanh_inplace": [I, P, L, P],
     "pe_wkv_recurrence": [I, P, P, P, P, L, P, P, P, P, F, P, P, P, P, I, P, P, I, I, I, I, I, I, I, P, P, P],
     "pe_qkv_rotate_append": [I, P, L, I, I, I, I, I, P, P, F, P, P, I, I, I, I, P, P, I, I, I, P, P, P, P, P, I, I, P, P,
-                             I, P, P],
+                             I, P, P, P],
     "pe_attention_generic_ex": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, P, P, I, I, I, P, P, P, P, I, I, P, P, P,
                                 I, I, P, P],
     "pe_attention_mma_ex": [I, P, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
@@ -81,8 +81,8 @@ _SIGNATURES = {
     "pe_embed_pair_gather": [I, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, P, P],
     "pe_rmsnorm_residual_sum": [I, P, P, P, I, P, P, P, I, I, F, P],
     "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
-    "pe_short_conv_silu": [I, P, L, I, P, I, P, P, P, P, P, I, I, I, I, P, P],
-    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P],
+    "pe_short_conv_silu": [I, P, L, I, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
+    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, P, P],
     "pe_moe_route": [P, P, I, I, I, P, P, P, I, P],
     "pe_moe_group": [P, I, I, I, P, P, P, P],
     "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
@@ -90,8 +90,15 @@ _SIGNATURES = {
     "pe_moe_combine": [I, P, P, P, P, P, I, P, I, I, P],
     "pe_glu_act": [I, P, P, I, I, I, F, F, P],
     "pe_moe_route_logits": [P, P, I, I, I, P, P, P, I, P],
-    "pe_attention_generic_masked": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, I, I, I, I, P, P, I, I, I, P, P, P, P, I, I,
+    "pe_attention_generic_masked": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, I, I, I, I, I, P, P, I, I, I, P, P, P, P, I, I,
                                     P, P, P, I, I, P, P],
+    "pe_embed_gather_scaled": [I, P, P, P, I, I, I, F, P, P, P],
+    "pe_moe_route_sigmoid_groups": [P, I, I, I, I, I, P, P, P, I, P],
+    "pe_ssd_recurrence": [I, P, L, P, L, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, P, P, P],
+    "pe_gated_part_norm": [I, P, P, L, P, F, P, I, I, I, P],
+    "pe_dyt": [I, I, P, P, P, P, F, P, I, I, P],
+    "pe_dyt_add": [I, P, P, P, P, F, P, P, F, P, I, I, P],
+    "pe_rmsnorm_pair_mix": [I, P, P, P, P, F, F, F, P, I, I, P],
     "pe_norm_token_shift": [I, P, P, F, P, P, P, P, P, P, I, I, I, P, P],
     "pe_depth_average": [P, L, P, I, P, P, L, P],
     "pe_polynorm": [I, P, P, F, P, I, I, P],
@@ -106,6 +113,7 @@ _RESTYPES = {"pe_wait_limit_polls": (L, []),
              "pe_wkv_scratch_floats": (L, [I, I, I, I]),
              "pe_mlstm_scratch_floats": (L, [I, I, I, I, I]),
              "pe_delta_rule_scratch_floats": (L, [I, I, I, I, I]),
+             "pe_ssd_scratch_floats": (L, [I, I, I, I, I]),
              "pe_sample_scratch_bytes": (L, [I, I, F, I, F, F])}
 
 

@@ -58,12 +58,15 @@ def _need(cond: bool, msg: str) -> None:
         raise KernelError(msg)
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor) -> None:
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, status: torch.Tensor, scale: float = 1.0,
+                 copy: Optional[torch.Tensor] = None) -> None:
+    """``out = table[ids] * scale`` (float32); ``copy`` (float32, the shape of ``out``) gets the same rows."""
     _need(ids.dtype == torch.int32 and out.dtype == torch.float32, "embed_gather: ids int32, out float32")
     _need(table.is_contiguous() and out.is_contiguous() and ids.is_contiguous(), "embed_gather: contiguous tensors")
+    _need(copy is None or (copy.dtype == torch.float32 and copy.is_contiguous() and copy.shape == out.shape), "embed_gather: copy")
     n, hidden = out.shape
-    check(library().pe_embed_gather(dtype_tag(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n, hidden,
-                                    table.shape[0], _ptr(status), _stream()), "embed_gather")
+    check(library().pe_embed_gather_scaled(dtype_tag(table.dtype), _ptr(table), _ptr(ids), _ptr(out), n, hidden,
+                                           table.shape[0], float(scale), _ptr(copy), _ptr(status), _stream()), "embed_gather")
     _count(1)
 
 
@@ -179,12 +182,13 @@ def qkv_rotate_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads
                       v_interleaved: bool, token_seq: torch.Tensor, token_pos: torch.Tensor, seq_slot: torch.Tensor,
                       seq_qstart: torch.Tensor, page_table: Optional[torch.Tensor], num_pages: int,
                       k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], write_cache: bool,
-                      status: torch.Tensor) -> None:
+                      status: torch.Tensor, bias: Optional[torch.Tensor] = None) -> None:
     """The general form of ``qk_norm_rope_append`` (csrc/rope_append.cu): either layout of rotated pairs, values of
     their own size that may be divided by their root mean square and rotated by their position on the way to the
-    cache.  ``qkv`` rows: q heads | k heads | v heads."""
+    cache.  ``qkv`` rows: q heads | k heads | v heads.  ``bias`` (float32, one per q|k|v feature) is added first."""
     _need(qkv.stride(-1) == 1, "qkv_rotate_append: rows of qkv must be contiguous")
-    for t in (cos, sin, v_cos, v_sin, q_norm_w, k_norm_w):
+    _need(bias is None or bias.numel() == (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_dim, "qkv_rotate_append: bias size")
+    for t in (cos, sin, v_cos, v_sin, q_norm_w, k_norm_w, bias):
         _need(t is None or (t.dtype == torch.float32 and t.is_contiguous()), "qkv_rotate_append: float32 tables and weights")
     check(library().pe_qkv_rotate_append(
         dtype_tag(qkv.dtype), _ptr(qkv), qkv.stride(0), n_tokens, n_heads, n_kv_heads, head_dim, v_dim,
@@ -193,7 +197,7 @@ def qkv_rotate_append(qkv: torch.Tensor, n_tokens: int, n_heads: int, n_kv_heads
         v_rotary_dim if v_cos is not None else 0, 0 if v_cos is None else v_cos.shape[0], 1 if v_interleaved else 0,
         _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot), _ptr(seq_qstart), _ptr(page_table),
         0 if page_table is None else page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages),
-        1 if write_cache else 0, _ptr(status), _stream()), "qkv_rotate_append")
+        1 if write_cache else 0, _ptr(bias), _ptr(status), _stream()), "qkv_rotate_append")
     _count(1)
 
 
@@ -671,14 +675,16 @@ def mlstm_scratch_floats(n_seqs: int, heads: int, d: int, dv: int, max_chunks: i
 
 
 def short_conv_silu(x: torch.Tensor, col0: int, w: torch.Tensor, tail: torch.Tensor, token_seq: torch.Tensor,
-                    seq_slot: torch.Tensor, seq_qstart: torch.Tensor, out: torch.Tensor, n_seqs: int, status: torch.Tensor) -> None:
-    """Causal convolution over time per channel, then silu; ``tail [slots, taps - 1, channels]`` float32 carries every
-    sequence's last inputs between steps and is brought up to date (csrc/delta_rule.cu)."""
+                    seq_slot: torch.Tensor, seq_qstart: torch.Tensor, out: torch.Tensor, n_seqs: int, status: torch.Tensor,
+                    bias: Optional[torch.Tensor] = None) -> None:
+    """Causal convolution over time per channel (plus ``bias``, float32 per channel), then silu; ``tail [slots, taps - 1,
+    channels]`` float32 carries every sequence's last inputs between steps and is brought up to date (csrc/delta_rule.cu)."""
     channels, taps = w.shape
+    _need(bias is None or (bias.dtype == torch.float32 and bias.is_contiguous() and bias.numel() == channels), "short_conv: bias")
     _need(w.dtype == torch.float32 and w.is_contiguous() and tail.dtype == torch.float32 and tail.is_contiguous(), "short_conv: w, tail f32")
     _need(x.stride(1) == 1 and out.is_contiguous() and out.shape == (x.shape[0], channels) and out.dtype == x.dtype, "short_conv: shapes")
     _need(taps == 1 or tuple(tail.shape[1:]) == (taps - 1, channels), "short_conv: tail shape")
-    check(library().pe_short_conv_silu(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(col0), _ptr(w), taps, _ptr(tail),
+    check(library().pe_short_conv_silu(dtype_tag(x.dtype), _ptr(x), x.stride(0), int(col0), _ptr(w), _ptr(bias), taps, _ptr(tail),
                                        _ptr(token_seq), _ptr(seq_slot), _ptr(seq_qstart), _ptr(out), x.shape[0], n_seqs, channels,
                                        tail.shape[0] if taps > 1 else (1 << 30), _ptr(status), _stream()), "short_conv_silu")
     _count(2 if taps > 1 else 1)
@@ -688,17 +694,20 @@ def delta_rule_recurrence(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Ten
                           gate: torch.Tensor, norm_w: torch.Tensor, eps: float, q_scale: float, out: torch.Tensor,
                           S: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, max_q: int, heads: int,
                           kv_heads: int, d: int, dv: int, status: torch.Tensor, chunk: int = 0, max_chunks: int = 1,
-                          scratch: Optional[torch.Tensor] = None) -> None:
+                          scratch: Optional[torch.Tensor] = None, head_decay: bool = False, gate_silu: bool = False) -> None:
     """csrc/delta_rule.cu.  ``qkv [N, 2 * kv_heads * d + heads * dv]`` after the convolutions; ``a [N, heads * d]`` and
     ``b [N, heads]`` float32; ``gate [N, heads * dv]`` in the run dtype (any row stride).  ``chunk`` > 0: prompts cut into
-    chunks of that many tokens that run side by side (``scratch``: float32, ``delta_rule_scratch_floats`` of them)."""
+    chunks of that many tokens that run side by side (``scratch``: float32, ``delta_rule_scratch_floats`` of them).
+    ``head_decay``: one decay per head (``a [N, heads]``, ``dt_bias [heads]``); ``gate_silu``: silu instead of sigmoid."""
+    _need(a.shape[1] == (heads if head_decay else heads * d) and dt_bias.numel() == a.shape[1], "delta_rule: the decay's layout")
     _need(qkv.is_contiguous() and qkv.shape[1] == 2 * kv_heads * d + heads * dv, "delta_rule: q|k|v layout")
     _need(a.dtype == torch.float32 and a.is_contiguous() and b.dtype == torch.float32 and b.is_contiguous(), "delta_rule: a, b f32")
     _need(gate.stride(1) == 1 and gate.dtype == qkv.dtype and out.is_contiguous() and S.is_contiguous(), "delta_rule: layouts")
     check(library().pe_delta_rule_recurrence(dtype_tag(qkv.dtype), _ptr(qkv), _ptr(a), _ptr(dt_bias), _ptr(A_log), _ptr(b),
                                              _ptr(gate), gate.stride(0), _ptr(norm_w), float(eps), float(q_scale), _ptr(out),
                                              _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, int(max_q), heads, kv_heads, d, dv,
-                                             S.shape[0], int(chunk), int(max_chunks), _ptr(scratch), _ptr(status), _stream()),
+                                             S.shape[0], int(chunk), int(max_chunks), _ptr(scratch), 1 if head_decay else 0,
+                                             1 if gate_silu else 0, _ptr(status), _stream()),
           "delta_rule_recurrence")
     _count(3 if chunk > 0 else 1)
 
@@ -791,9 +800,10 @@ def attention_generic_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n
                              seq_past: torch.Tensor, seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int,
                              k_pages: torch.Tensor, v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int,
                              max_splits: int, status: torch.Tensor, *, window: int = 0, chunk: int = 0,
-                             v_ld: Optional[int] = None, v_heads: Optional[int] = None) -> None:
+                             v_ld: Optional[int] = None, v_heads: Optional[int] = None, keep_first: int = 0) -> None:
     """``attention_generic_ex`` with a chunk mask (``chunk`` > 0: a query sees the keys of its own block of that many
-    positions, blocks counted from the sequence's start), value rows ``v_ld`` elements apart (values that are the leading
+    positions, blocks counted from the sequence's start), kept first keys (``keep_first`` > 0 with a ``window``: positions
+    below it stay visible to every later query), value rows ``v_ld`` elements apart (values that are the leading
     ``v_dim`` features of wider rows) and ``v_heads`` value heads a page (kv head g reads value head ``g % v_heads``)."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
     _need(q.dtype == k_pages.dtype == v_pages.dtype and out.dtype in (q.dtype, torch.float32),
@@ -802,7 +812,7 @@ def attention_generic_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n
     v_heads = n_kv_heads if v_heads is None else int(v_heads)
     check(library().pe_attention_generic_masked(
         dtype_tag(q.dtype), 1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads,
-        n_kv_heads, head_dim, v_dim, float(scale), int(window), int(chunk), v_ld, v_heads,
+        n_kv_heads, head_dim, v_dim, float(scale), int(window), int(chunk), int(keep_first), v_ld, v_heads,
         1 if (out.dtype == torch.float32 and q.dtype != torch.float32) else 0, 0, None, None, 0, 0, 0,
         _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot), _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages),
         _ptr(v_pages), _ptr(scratch), split_keys, max_splits, _ptr(status), _stream()), "attention_generic_masked")
@@ -917,4 +927,96 @@ def latent_prepare(x: torch.Tensor, q_col0: int, low_col0: int, heads: int, d: i
                                       cos.shape[0] if rot else 0, x.shape[0], _ptr(token_seq), _ptr(token_pos), _ptr(seq_slot),
                                       _ptr(page_table), page_table.shape[1], num_pages, _ptr(pages), _ptr(qfull), _ptr(absorbed),
                                       1 if write_cache else 0, _ptr(status), _stream()), "latent_prepare")
+    _count(1)
+
+
+def moe_route_sigmoid_groups(logits: torch.Tensor, top: int, n_groups: int, keep: int, chosen: torch.Tensor, weight: torch.Tensor,
+                             dense_rows: Optional[torch.Tensor] = None, n_real: int = 0) -> None:
+    """Scores ``sigmoid(logits)``; the outputs form ``n_groups`` equal groups of neighbours, a group scores the sum of its two
+    largest, only the ``keep`` best groups may be chosen from; the ``top`` largest scores among them, weighted with the score
+    itself (csrc/moe.cu).  ``n_groups`` <= 1: no groups."""
+    _need(logits.dtype == torch.float32 and logits.is_contiguous(), "moe_route_sigmoid_groups: float32 logits")
+    n, n_all = logits.shape
+    _need(chosen.dtype == torch.int32 and weight.dtype == torch.float32 and chosen.numel() == n * top == weight.numel(),
+          "moe_route_sigmoid_groups: outputs")
+    _need(dense_rows is None or (dense_rows.dtype == torch.int32 and dense_rows.numel() == n * top), "moe_route_sigmoid_groups: dense_rows")
+    check(library().pe_moe_route_sigmoid_groups(_ptr(logits), n, n_all, int(top), int(n_groups), int(keep), _ptr(chosen), _ptr(weight),
+                                                _ptr(dense_rows), int(n_real), _stream()), "moe_route_sigmoid_groups")
+    _count(1)
+
+
+# ---- state-space recurrence ---------------------------------------------------------------------------------------------
+def ssd_scratch_floats(n_seqs: int, heads: int, n: int, dv: int, max_chunks: int) -> int:
+    return int(library().pe_ssd_scratch_floats(n_seqs, heads, n, dv, max_chunks))
+
+
+def ssd_recurrence(xbc: torch.Tensor, dt: torch.Tensor, dt_bias: torch.Tensor, A_log: torch.Tensor, D: torch.Tensor, y: torch.Tensor,
+                   S: torch.Tensor, seq_slot: torch.Tensor, seq_qstart: torch.Tensor, n_seqs: int, max_q: int, heads: int,
+                   groups: int, n: int, dv: int, status: torch.Tensor, chunk: int = 0, max_chunks: int = 1,
+                   scratch: Optional[torch.Tensor] = None) -> None:
+    """csrc/ssd.cu.  ``xbc [N, heads * dv + 2 * groups * n]`` after the convolution (x | B | C, any row stride), ``dt [N, heads]``
+    in the run dtype (any row stride), ``y [N, heads * dv]`` float32, ``S [slots, heads, n, dv]`` float32."""
+    _need(xbc.stride(1) == 1 and dt.stride(1) == 1 and xbc.dtype == dt.dtype, "ssd: rows of xbc and dt contiguous, one dtype")
+    _need(xbc.shape[1] == heads * dv + 2 * groups * n and dt.shape[1] == heads, "ssd: x|B|C and dt layout")
+    _need(y.dtype == torch.float32 and y.is_contiguous() and S.dtype == torch.float32 and S.is_contiguous(), "ssd: y, S f32")
+    for t in (dt_bias, A_log, D):
+        _need(t.dtype == torch.float32 and t.numel() == heads, "ssd: dt_bias, A_log, D float32, one per head")
+    check(library().pe_ssd_recurrence(dtype_tag(xbc.dtype), _ptr(xbc), xbc.stride(0), _ptr(dt), dt.stride(0), _ptr(dt_bias),
+                                      _ptr(A_log), _ptr(D), _ptr(y), _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, int(max_q),
+                                      heads, groups, n, dv, S.shape[0], int(chunk), int(max_chunks), _ptr(scratch), _ptr(status),
+                                      _stream()), "ssd_recurrence")
+    _count(3 if chunk > 0 else 1)
+
+
+def gated_part_norm(y: torch.Tensor, z: torch.Tensor, w: torch.Tensor, eps: float, out: torch.Tensor, parts: int) -> None:
+    """``v = y * silu(z)``; each of ``parts`` equal parts of a row divided by its root mean square, times ``w`` (csrc/ssd.cu).
+    ``y`` float32, ``z`` and ``out`` in the run dtype (``z`` with any row stride)."""
+    n, width = y.shape
+    _need(y.dtype == torch.float32 and y.is_contiguous() and out.is_contiguous() and z.stride(1) == 1 and z.dtype == out.dtype
+          and tuple(out.shape) == (n, width) and tuple(z.shape) == (n, width), "gated_part_norm: shapes and dtypes")
+    _need(w.dtype == torch.float32 and w.numel() == width and width % parts == 0, "gated_part_norm: weight, parts")
+    check(library().pe_gated_part_norm(dtype_tag(out.dtype), _ptr(y), _ptr(z), z.stride(0), _ptr(w), float(eps), _ptr(out), n,
+                                       width, int(parts), _stream()), "gated_part_norm")
+    _count(1)
+
+
+# ---- the norm without statistics ----------------------------------------------------------------------------------------
+def dyt(x: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: float, out: torch.Tensor,
+        rows: Optional[torch.Tensor] = None) -> None:
+    """``out = tanh(alpha * x) * w + b`` (csrc/dyt.cu); ``x`` float32 or of ``out``'s dtype; ``rows``: gather those rows of x."""
+    n, dim = out.shape
+    _need(x.is_contiguous() and out.is_contiguous() and x.shape[1] == dim and x.dtype in (torch.float32, out.dtype), "dyt: shapes")
+    _need(w.dtype == torch.float32 and b.dtype == torch.float32 and w.numel() == dim == b.numel(), "dyt: weight and bias float32")
+    _need(rows is None or (rows.dtype == torch.int32 and rows.numel() >= n), "dyt: rows int32")
+    check(library().pe_dyt(dtype_tag(out.dtype), 1 if x.dtype == torch.float32 else 0, _ptr(x), _ptr(rows), _ptr(w), _ptr(b),
+                           float(alpha), _ptr(out), n, dim, _stream()), "dyt")
+    _count(1)
+
+
+def dyt_add(stream: torch.Tensor, delta: torch.Tensor, w: torch.Tensor, b: torch.Tensor, alpha: float,
+            next_norm=None, out: Optional[torch.Tensor] = None) -> None:
+    """``stream += tanh(alpha * delta) * w + b``; with ``next_norm = (w2, b2, alpha2)`` and ``out``: ``out = tanh(alpha2 *
+    stream) * w2 + b2`` of the new rows in the same pass (csrc/dyt.cu)."""
+    n, dim = stream.shape
+    _need(stream.dtype == torch.float32 and stream.is_contiguous() and delta.is_contiguous() and tuple(delta.shape) == (n, dim),
+          "dyt_add: shapes")
+    w2 = b2 = None
+    a2 = 0.0
+    if out is not None:
+        w2, b2, a2 = next_norm
+        _need(out.dtype == delta.dtype and out.is_contiguous() and tuple(out.shape) == (n, dim), "dyt_add: out")
+    check(library().pe_dyt_add(dtype_tag(delta.dtype), _ptr(stream), _ptr(delta), _ptr(w), _ptr(b), float(alpha), _ptr(w2), _ptr(b2),
+                               float(a2), _ptr(out), n, dim, _stream()), "dyt_add")
+    _count(1)
+
+
+def rmsnorm_pair_mix(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, sa: float, sb: float,
+                     out: torch.Tensor) -> None:
+    """``out = sa * unit(a) * wa + sb * unit(b) * wb`` row by row (csrc/dyt.cu)."""
+    n, dim = a.shape
+    _need(a.is_contiguous() and b.is_contiguous() and out.is_contiguous() and a.shape == b.shape == out.shape
+          and a.dtype == b.dtype == out.dtype, "rmsnorm_pair_mix: shapes and dtypes")
+    _need(wa.dtype == torch.float32 and wb.dtype == torch.float32 and wa.numel() == dim == wb.numel(), "rmsnorm_pair_mix: weights")
+    check(library().pe_rmsnorm_pair_mix(dtype_tag(a.dtype), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(eps), float(sa), float(sb),
+                                        _ptr(out), n, dim, _stream()), "rmsnorm_pair_mix")
     _count(1)

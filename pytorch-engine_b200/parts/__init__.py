@@ -4,7 +4,7 @@ from . import registry, spec
 from .registry import lookup, register, registered, unregister
 from .spec import BlockSpec, CacheRequest, ModelPlan, PartSpec, RunStep, WeightDecl
 from .runtime import Runtime
-from . import norm, rope, attention, swiglu, embedding, block, wkv, token_gate, mlstm, delta_rule, moe, stream_parts, dense_ff, latent_attention, diff_attention  # noqa: F401  (registers the built-in kinds)
+from . import norm, rope, attention, swiglu, embedding, block, wkv, token_gate, mlstm, delta_rule, moe, stream_parts, dense_ff, latent_attention, diff_attention, ssd  # noqa: F401  (registers the built-in kinds)
 
 __all__ = ["registry", "spec", "lookup", "register", "registered", "unregister", "BlockSpec", "CacheRequest",
            "ModelPlan", "PartSpec", "RunStep", "WeightDecl", "Runtime"]

@@ -35,8 +35,12 @@ class GQAttention:
     head's value is divided by its root mean square, eps inside the root, no weight; it is cached so),
     ``value_position`` (name of a rotary encoding of the plan over the value's features: the value of position j is
     cached turned by j, and each head's output at position i is turned back by i before the output projection).
-    A rotary ``position`` may use either layout of pairs.  With any of these the mixer runs on the general kernels
-    (``qkv_rotate_append``, ``attention_generic_ex``) unless a tensor-core kernel takes the case."""
+    A rotary ``position`` may use either layout of pairs.  ``bias`` (true: q, k and v have biases ``q_bias, k_bias, v_bias``,
+    added in float32 before anything else), ``keep_first`` (with a ``window``: the first that many positions of a sequence stay
+    visible to every later query, at their own positions), ``output_gate`` ("sigmoid": the joined heads are multiplied feature
+    by feature with ``sigmoid(g_proj x)`` before the output projection; the gate's product rides in the q|k|v product).
+    With any of these the mixer runs on the general kernels (``qkv_rotate_append``, ``attention_generic_ex``) unless a
+    tensor-core kernel takes the case."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
@@ -53,6 +57,10 @@ class GQAttention:
         if params.get("qk_norm", False):
             decls["q_norm"] = WeightDecl((d,), "norm")
             decls["k_norm"] = WeightDecl((d,), "norm")
+        if params.get("bias", False):
+            decls.update({"q_bias": WeightDecl((nh * d,)), "k_bias": WeightDecl((nkv * d,)), "v_bias": WeightDecl((nkv * dv,))})
+        if params.get("output_gate"):
+            decls["g_proj"] = WeightDecl((nh * dv, h))
         return decls
 
     @classmethod
@@ -60,7 +68,8 @@ class GQAttention:
         d = int(params["head_dim"])
         dv = int(params.get("v_head_dim") or d)
         return CacheRequest(kind="kv", kv_heads=int(params["n_kv_heads"]), head_dim=d, window=params.get("window"),
-                            v_head_dim=None if dv == d else dv)
+                            v_head_dim=None if dv == d else dv,
+                            keep_first=int(params.get("keep_first") or 0) if params.get("window") else 0)
 
     def __init__(self, params, weights, runtime, positions=None) -> None:
         self.runtime = runtime
@@ -81,7 +90,18 @@ class GQAttention:
         scale = params.get("scale")
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.window = int(params["window"]) if params.get("window") else 0
-        self.qkv = fuse_rows(runtime, [weights["q_proj"], weights["k_proj"], weights["v_proj"]])
+        self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        self.output_gate = params.get("output_gate")
+        if self.output_gate not in (None, "sigmoid"):
+            raise ValueError(f"output_gate {self.output_gate!r} is not built (None or 'sigmoid')")
+        self.bias = None
+        if params.get("bias", False):
+            self.bias = torch.cat([weights[n].to(device=runtime.device, dtype=torch.float32).reshape(-1)
+                                   for n in ("q_bias", "k_bias", "v_bias")]).contiguous()
+        fused = [weights["q_proj"], weights["k_proj"], weights["v_proj"]]
+        if self.output_gate:
+            fused.append(weights["g_proj"])       # q | k | v | gate: one product over the mixer's input
+        self.qkv = fuse_rows(runtime, fused)
         self.o_proj = runtime.adopt(weights["o_proj"])
         self.q_norm = self.k_norm = None
         if params.get("qk_norm", False):
@@ -108,17 +128,20 @@ class GQAttention:
         interleaved = self.fused_position and getattr(self.position, "interleaved", False)
         # what the kernels of the plain softmax attention do not do
         self.general = bool(self.sink or self.v_norm or self.value_position is not None or self.v_dim != self.head_dim
-                            or interleaved)
+                            or interleaved or self.bias is not None or self.keep_first or self.output_gate)
         if self.general and self.position is not None and not self.fused_position:
             raise ValueError("the general attention path takes a rotary position encoding with tables(), or none")
         self.qkv_dim = (self.n_heads + self.n_kv_heads) * self.head_dim + self.n_kv_heads * self.v_dim
+        self.gate_col = self.qkv_dim               # the gate's columns follow q | k | v in the fused product
+        if self.output_gate:
+            self.qkv_dim += self.n_heads * self.v_dim
         # tensor-core kernels where they take the shape (bfloat16, head size 64 or 128, group <= 16);
         # the generic float32-arithmetic kernels otherwise
         # (with a sink or turned values too, if keys and values have one size and the values turn in interleaved pairs
         # over the whole head: these kernels take both in their epilogues)
         vp = self.value_position
-        fast_ok = self.v_dim == self.head_dim and (vp is None or (getattr(vp, "interleaved", False)
-                                                                  and vp.tables()[2] == self.v_dim))
+        fast_ok = self.v_dim == self.head_dim and not self.keep_first and (
+            vp is None or (getattr(vp, "interleaved", False) and vp.tables()[2] == self.v_dim))
         self.use_mma = (fast_ok and runtime.is_cuda
                         and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
         # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, groups up to 32)
@@ -137,6 +160,10 @@ class GQAttention:
             self.rotate_append_general(qkv, n, ctx, view, writes_cache)
             out = ctx.buffer("attn.out", (n, self.n_heads * self.v_dim), rt.dtype)
             self.attend_general(qkv, out, ctx, view)
+            if self.output_gate:
+                gated = ctx.buffer("attn.gated", (n, self.n_heads * self.v_dim), rt.dtype)
+                ops.sigmoid_gate(out.view(n, self.n_heads, self.v_dim).transpose(0, 1), qkv[:, self.gate_col:], gated)
+                out = gated
             delta = ctx.buffer("attn.delta", (n, self.hidden), rt.dtype)
             rt.linear(out, self.o_proj, out=delta)
             return delta
@@ -173,7 +200,7 @@ class GQAttention:
         ops.qkv_rotate_append(qkv, n, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim, self.q_norm, self.k_norm,
                               self.eps, cos, sin, rot, inter, self.v_norm == "unit", vcos, vsin, vrot, vinter,
                               ctx.token_seq, ctx.token_pos, ctx.seq_slot, ctx.seq_qstart, view.page_table, view.num_pages,
-                              view.k_pages, view.v_pages, writes_cache, self.runtime.status)
+                              view.k_pages, view.v_pages, writes_cache, self.runtime.status, self.bias)
 
     def attend_general(self, q: torch.Tensor, out: torch.Tensor, ctx, view) -> None:
         vcos = vsin = None
@@ -208,6 +235,13 @@ class GQAttention:
             scratch = ctx.buffer(
                 "attn.scratch",
                 (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.v_dim, max_splits),), torch.float32)
+        if self.keep_first:
+            ops.attention_generic_masked(
+                ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim,
+                self.scale, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot, view.page_table, view.num_pages, view.k_pages,
+                view.v_pages, scratch, SPLIT_KEYS, max_splits, self.runtime.status, window=self.window,
+                keep_first=self.keep_first)
+            return
         ops.attention_generic_ex(
             ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim, self.v_dim,
             self.scale, self.window, self.sink, vcos, vsin, vrot, vinter, ctx.seq_qstart, ctx.seq_past, ctx.seq_slot,

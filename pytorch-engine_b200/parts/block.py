@@ -197,3 +197,76 @@ class SandwichDepthBlock:
         ctx.depth_rows_ready = None if last else self.index + 2
         ctx.stream_copy = None
         return None
+
+
+@register("arrangement", "sandwich")
+class SandwichBlock:
+    """A norm before and after each sublayer:
+
+        x = x + post_mixer_norm(mixer(mixer_norm(x)))
+        x = x + post_ffn_norm(ffn(ffn_norm(x)))                   (if the block has a feed-forward)
+
+    Parts by name: ``mixer_norm, post_mixer_norm``, one mixer (``mixer``) or two that read the same input (any two names of
+    role "mixer", with ``combine``, a part that makes one output of the two), optionally ``ffn_norm, ffn, post_ffn_norm``, and
+    optionally ``inject``: a part of role "stream" that rewrites the stream in front of the block (``inject.forward(stream,
+    ctx)``).  The block adds into the float32 stream itself and hands nothing on.  Where the post norm offers it
+    (``add_after(..., then=)``), the add behind the mixer and the norm in front of the feed-forward are one pass."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    def __init__(self, spec, parts, runtime) -> None:
+        self.runtime = runtime
+        self.name = spec.name
+        self.mixer_norm, self.post_mixer_norm = parts["mixer_norm"], parts["post_mixer_norm"]
+        self.mixer_names = list(spec.mixer_names())
+        self.mixers = [parts[n] for n in self.mixer_names]
+        if len(self.mixers) not in (1, 2):
+            raise ValueError("a sandwich block has one mixer, or two with a 'combine' part")
+        self.combine = parts.get("combine")
+        if len(self.mixers) == 2 and self.combine is None:
+            raise ValueError("a sandwich block with two mixers needs a 'combine' part")
+        self.ffn = parts.get("ffn")
+        self.ffn_norm, self.post_ffn_norm = parts.get("ffn_norm"), parts.get("post_ffn_norm")
+        self.inject = parts.get("inject")
+
+    def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
+        rt = self.runtime
+        if pending is not None:       # a block of another arrangement before this one left its last delta to be added
+            if isinstance(pending, DeltaSum):
+                pending.add_into(stream, stream)
+            else:
+                stream.add_(pending)
+        if self.inject is not None:
+            self.inject.forward(stream, ctx)
+        normed = ctx.buffer("block.normed", tuple(stream.shape), rt.dtype)
+        self.mixer_norm.add_forward(stream, None, normed)
+        outs = []
+        for i, (name, mixer) in enumerate(zip(self.mixer_names, self.mixers)):
+            v = view[name] if isinstance(view, dict) else view
+            out = mixer.forward(normed, ctx, v) if writes_cache else mixer.forward(normed, ctx, v, writes_cache=False)
+            if any(type(m) is type(mixer) for m in self.mixers[i + 1:]):
+                # a part's delta lies in a buffer that the next part of its class uses again
+                keep = ctx.buffer(f"block.delta{i}", tuple(out.shape), out.dtype)
+                keep.copy_(out)
+                out = keep
+            outs.append(out)
+        mixed = outs[0]
+        if len(outs) == 2:
+            mixed = self.combine.forward(outs[0], outs[1], ctx.buffer("block.mixed", tuple(outs[0].shape), outs[0].dtype))
+        if self.ffn is None:
+            self.post_mixer_norm.add_after(stream, mixed, None)
+            ctx.stream_copy = None
+            return None
+        if self.fuses(self.post_mixer_norm, self.ffn_norm):
+            self.post_mixer_norm.add_after(stream, mixed, normed, then=self.ffn_norm)
+        else:
+            self.post_mixer_norm.add_after(stream, mixed, None)
+            self.ffn_norm.add_forward(stream, None, normed)
+        self.post_ffn_norm.add_after(stream, self.ffn.forward(normed, ctx), None)
+        ctx.stream_copy = None
+        return None
+
+    @staticmethod
+    def fuses(post_norm, next_norm) -> bool:
+        import inspect
+        return type(post_norm) is type(next_norm) and "then" in inspect.signature(post_norm.add_after).parameters

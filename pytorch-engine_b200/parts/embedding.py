@@ -12,10 +12,11 @@ from .spec import CacheRequest, WeightDecl
 
 @register("embedding", "token_embedding")
 class TokenEmbedding:
-    """params: ``vocab``, ``hidden``.  weights: ``weight [vocab, hidden]``.  Output: the float32
-    residual stream (pygguf_engine/model.py:2237, pygguf_engine/quant_kernels.py:1846-1847)."""
+    """params: ``vocab``, ``hidden``, optionally ``scale`` (a factor on every row).  weights: ``weight [vocab, hidden]``.
+    Output: the float32 residual stream (pygguf_engine/model.py:2237, pygguf_engine/quant_kernels.py:1846-1847)."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
+    writes_copy = True  # forward() can leave a second copy of its rows
 
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
@@ -25,10 +26,11 @@ class TokenEmbedding:
         self.runtime = runtime
         self.vocab = int(params["vocab"])
         self.hidden = int(params["hidden"])
+        self.scale = float(params.get("scale", 1.0) or 1.0)
         self.weight = runtime.adopt(weights["weight"])
 
-    def forward(self, token_ids: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
-        ops.embed_gather(self.weight, token_ids, out, self.runtime.status)
+    def forward(self, token_ids: torch.Tensor, out: torch.Tensor, copy=None) -> torch.Tensor:
+        ops.embed_gather(self.weight, token_ids, out, self.runtime.status, self.scale, copy)
         return out
 
 

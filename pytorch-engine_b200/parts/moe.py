@@ -7,7 +7,10 @@ that return their input, optionally with a shared expert that every token passes
     expert(h) = D act(G h, U h)  with the activations of ``parts/swiglu.py``
 
 With ``choice = "top_logits"`` the router instead takes the ``top`` largest of ``z + bias`` and weights them by a softmax
-over the chosen ones alone (no correction).
+over the chosen ones alone (no correction).  With ``choice = "sigmoid_groups"`` the scores are ``s = sigmoid(z)``; the
+experts form ``groups`` equal groups of neighbours, a group scores the sum of its two largest ``s``, and only experts of the
+``keep_groups`` best groups can be chosen: the ``top`` largest ``s`` among them, weighted with ``s`` itself (no weights beside
+the router's matrix).
 
 The (token, choice) pairs are grouped by expert on the device and every expert's rows go through its matrices in one
 launch per product, so nothing is read back to the host and a decode step stays recordable.  A handful of pairs (a
@@ -48,7 +51,8 @@ class RoutedExperts:
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:
         h, n, extra, inter = (int(params[k]) for k in ("hidden", "n_experts", "n_identity", "intermediate"))
         decls = {"router": WeightDecl((n + extra, h))}
-        decls["router_bias" if params.get("choice") == "top_logits" else "correction"] = WeightDecl((n + extra,))
+        if params.get("choice") != "sigmoid_groups":
+            decls["router_bias" if params.get("choice") == "top_logits" else "correction"] = WeightDecl((n + extra,))
         for e in range(n):
             decls[f"e{e}.gate"] = WeightDecl((inter, h))
             decls[f"e{e}.up"] = WeightDecl((inter, h))
@@ -74,10 +78,16 @@ class RoutedExperts:
         dev, dt = runtime.device, runtime.dtype
         self.router = runtime.adopt(weights["router"])
         self.choice = str(params.get("choice") or "softmax_all")
-        if self.choice not in ("softmax_all", "top_logits"):
-            raise ValueError(f"router choice {self.choice!r} is not built ('softmax_all' and 'top_logits' are)")
+        if self.choice not in ("softmax_all", "top_logits", "sigmoid_groups"):
+            raise ValueError(f"router choice {self.choice!r} is not built ('softmax_all', 'top_logits' and 'sigmoid_groups' are)")
         self.correction = self.router_bias = None
-        if self.choice == "top_logits":
+        self.groups = int(params.get("groups") or 1)
+        self.keep_groups = int(params.get("keep_groups") or self.groups)
+        if self.choice == "sigmoid_groups":
+            n_all = self.n_experts + self.n_identity
+            if n_all % self.groups or not 1 <= self.keep_groups <= self.groups or self.top > self.keep_groups * (n_all // self.groups):
+                raise ValueError(f"{n_all} experts in {self.groups} groups of which {self.keep_groups} are kept cannot give {self.top} choices")
+        elif self.choice == "top_logits":
             self.router_bias = runtime.adopt(weights["router_bias"], torch.float32)
         else:
             self.correction = runtime.adopt(weights["correction"], torch.float32)
@@ -108,7 +118,9 @@ class RoutedExperts:
                 and ops.gemm_smallm_supported(x, self.gate_up.view(-1, self.hidden)))
 
     def route(self, logits, chosen, weight, dense_rows=None, n_real: int = 0) -> None:
-        if self.choice == "top_logits":
+        if self.choice == "sigmoid_groups":
+            ops.moe_route_sigmoid_groups(logits, self.top, self.groups, self.keep_groups, chosen, weight, dense_rows, n_real)
+        elif self.choice == "top_logits":
             ops.moe_route_logits(logits, self.router_bias, self.top, chosen, weight, dense_rows, n_real)
         else:
             ops.moe_route(logits, self.correction, self.top, chosen, weight, dense_rows, n_real)

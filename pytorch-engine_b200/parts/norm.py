@@ -1,4 +1,4 @@
-"""RMSNorm.  Formula: ``x * rsqrt(mean(x^2) + eps) * w`` in float32
+"""RMSNorm and Dynamic Tanh.  RMSNorm's formula: ``x * rsqrt(mean(x^2) + eps) * w`` in float32
 (pygguf_engine/quant_kernels.py:831-833, 1548; fused with the residual add 1595-1596)."""
 from __future__ import annotations
 
@@ -46,3 +46,47 @@ class RMSNorm:
     def add_after(self, stream: torch.Tensor, delta: torch.Tensor, cast: Optional[torch.Tensor] = None) -> None:
         """The norm on what is added: ``stream += rmsnorm(delta) * w``; ``cast`` gets the new rows in the run dtype."""
         ops.rmsnorm_add(stream, delta, self.weight, self.eps, cast)
+
+
+@register("norm", "dynamic_tanh")
+class DynamicTanh:
+    """A norm that computes no statistics: ``y = tanh(alpha * x) * weight + bias`` with one number ``alpha``, in float32
+    (csrc/dyt.cu).  params: ``dim``.  weights: ``weight [dim]``, ``bias [dim]``, ``alpha []``."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        dim = int(params["dim"])
+        return {"weight": WeightDecl((dim,), "norm"), "bias": WeightDecl((dim,)), "alpha": WeightDecl((), "unit")}
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.dim = int(params["dim"])
+        self.runtime = runtime
+        self.weight = runtime.adopt(weights["weight"], torch.float32)
+        self.bias = runtime.adopt(weights["bias"], torch.float32)
+        self.alpha = float(weights["alpha"].to(torch.float32).reshape(-1)[0].item())   # read once, when the model is built
+
+    def add_forward(self, residual: torch.Tensor, delta, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if delta is not None:
+            if hasattr(delta, "deltas"):
+                delta.add_into(residual, self.weight)
+            else:
+                residual.add_(delta)
+        ops.dyt(residual, self.weight, self.bias, self.alpha, out, rows)
+        return out
+
+    def forward(self, x: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        out = torch.empty_like(x) if out is None else out
+        ops.dyt(x, self.weight, self.bias, self.alpha, out)
+        return out
+
+    def add_after(self, stream: torch.Tensor, delta: torch.Tensor, cast: Optional[torch.Tensor] = None, then=None) -> None:
+        """The norm on what is added: ``stream += dyt(delta)``.  ``then`` (another norm of this kind) with ``cast``: ``cast``
+        gets ``then``'s norm of the new rows, in the same pass over them."""
+        if then is not None and cast is not None:
+            ops.dyt_add(stream, delta, self.weight, self.bias, self.alpha, (then.weight, then.bias, then.alpha), cast)
+            return
+        ops.dyt_add(stream, delta, self.weight, self.bias, self.alpha)
+        if cast is not None:
+            cast.copy_(stream)

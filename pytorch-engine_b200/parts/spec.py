@@ -103,6 +103,9 @@ class ModelPlan:
     # (``fnmatch``) of stored buffers that carry no weights
     duplicates: Mapping[str, str] = field(default_factory=dict)
     ignored: Tuple[str, ...] = ()
+    # true: the decoder keeps a float32 copy of the embedding's output for the length of a step (``ctx.embedding_output``),
+    # for a part that reads it again further down (an input that is mixed back into the stream)
+    keep_embedding_output: bool = False
 
     def part_specs(self):
         """Every PartSpec of the plan as (label, role, spec), for the weight loader and error texts."""
@@ -142,7 +145,7 @@ class CacheRequest:
 
     ``kind`` "kv": keys and values of every position, ``kv_heads x head_dim`` each (values
     ``kv_heads x v_head_dim`` when that is given and differs), and with ``window`` only the last
-    ``window`` positions need to stay; with ``chunk`` only the positions of the block of ``chunk`` positions that
+    ``window`` positions need to stay (and, with ``keep_first``, the first that many positions); with ``chunk`` only the positions of the block of ``chunk`` positions that
     the next query falls into.  ``value_heads``: the values have that many heads instead of ``kv_heads`` (several
     key maps over one set of values).  ``values_in_keys``: no values are stored; the mixer reads them out of the key
     rows (a latent cache whose row is both).  ``kind`` "state": tensors of fixed
@@ -159,6 +162,8 @@ class CacheRequest:
     chunk: Optional[int] = None
     value_heads: Optional[int] = None
     values_in_keys: bool = False
+    # with ``window``: the first ``keep_first`` positions stay visible to every later query, so their pages stay too
+    keep_first: int = 0
 
     @property
     def value_dim(self) -> int:
@@ -170,4 +175,4 @@ class CacheRequest:
 
     def group_key(self):
         return (self.kind, self.kv_heads, self.head_dim, self.window, self.state_shapes, self.value_dim, self.chunk,
-                self.n_value_heads, self.values_in_keys)
+                self.n_value_heads, self.values_in_keys, self.keep_first if self.window else 0)

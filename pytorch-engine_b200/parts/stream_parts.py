@@ -13,6 +13,12 @@ slot is taken.  It runs fused with the norm that produces ``h``, in float32, and
     x <- sum_{j = 0 .. i + 1} coeff[j] * X_j      (X_0: the embedding's output, X_(j+1): block j's result)
 
 with the results kept for the length of a step in one float32 buffer.
+
+``input_mix``: the stream is replaced by a learned mix of itself and the embedding's output, ``x <- W [x ; x0]`` (a block that
+runs several times over takes the model's input in again in front of every pass).
+
+``normed_mean``: two sublayer outputs side by side become one, ``(unit(a) * w_a + unit(b) * w_b) / 2``, each divided by its own
+root mean square over the row first.
 """
 from __future__ import annotations
 
@@ -69,4 +75,61 @@ class DepthAverage:
     def forward(self, results: torch.Tensor, out: torch.Tensor, copy: Optional[torch.Tensor] = None) -> torch.Tensor:
         """``results [>= terms, N, width]`` float32; ``out [N, width]`` gets the sum, and so does ``copy`` if given."""
         ops.depth_average(results, self.coeff, self.terms, out, copy)
+        return out
+
+
+@register("stream", "input_mix")
+class InputMix:
+    """``x <- W [x ; x0]`` with ``x0`` the embedding's output of this step (``ctx.embedding_output``; the plan sets
+    ``keep_embedding_output``).  params: ``dim``.  weights: ``weight [dim, 2 * dim]`` (the stream's half first).  The product's
+    inputs are in the run dtype, its result is written to the float32 stream."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        dim = int(params["dim"])
+        return {"weight": WeightDecl((dim, 2 * dim))}
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.dim = int(params["dim"])
+        self.weight = runtime.adopt(weights["weight"])
+
+    def forward(self, stream: torch.Tensor, ctx) -> torch.Tensor:
+        rt = self.runtime
+        x0 = getattr(ctx, "embedding_output", None)
+        if x0 is None:
+            raise ValueError("input_mix needs the embedding's output of the step (ModelPlan.keep_embedding_output)")
+        n, dim = stream.shape
+        both = ctx.buffer("input_mix.both", (n, 2 * dim), rt.dtype)
+        both[:, :dim].copy_(stream)
+        both[:, dim:].copy_(x0)
+        y = rt.linear(both, self.weight, out=stream, out_dtype=torch.float32)
+        if y.data_ptr() != stream.data_ptr():
+            stream.copy_(y)
+        return stream
+
+
+@register("stream", "normed_mean")
+class NormedMean:
+    """``out = scale * (unit(a) * w_a + unit(b) * w_b)`` (csrc/dyt.cu).  params: ``dim``, ``eps``, ``scale`` (default one half).
+    weights: ``weight_a [dim]``, ``weight_b [dim]``."""
+
+    graph_safe = True  # launches only; nothing in forward() waits for the device
+
+    @classmethod
+    def weight_decls(cls, params) -> Dict[str, WeightDecl]:
+        dim = int(params["dim"])
+        return {"weight_a": WeightDecl((dim,), "norm"), "weight_b": WeightDecl((dim,), "norm")}
+
+    def __init__(self, params, weights, runtime) -> None:
+        self.runtime = runtime
+        self.eps = float(params["eps"])
+        self.scale = float(params.get("scale", 0.5))
+        self.weight_a = runtime.adopt(weights["weight_a"], torch.float32)
+        self.weight_b = runtime.adopt(weights["weight_b"], torch.float32)
+
+    def forward(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
+        ops.rmsnorm_pair_mix(a, b, self.weight_a, self.weight_b, self.eps, self.scale, self.scale, out)
         return out
