@@ -236,6 +236,8 @@ int pe_dyt_add(int dtype, float* stream_rows, const void* delta, const float* w1
 int pe_rmsnorm_pair_mix(int dtype, const void* a, const void* b, const float* wa, const float* wb, float eps, float sa,
     float sb, void* out, int n_rows, int dim, cudaStream_t stream);
 
+int pe_concat_split(int dtype, const float* a, const float* b, void* hi, void* lo, int n_rows, int dim, cudaStream_t stream);
+
 // wait_probe.cu
 int pe_wait_probe(unsigned long long* out, int polls, cudaStream_t stream);
 long long pe_wait_limit_polls();

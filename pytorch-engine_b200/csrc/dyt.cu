@@ -1,11 +1,12 @@
 // Dynamic Tanh, a norm without statistics:  y = tanh(alpha * x) * w + b  (alpha one number, w and b per feature), in
 // float32 arithmetic; and the two things a block with a norm on either side of each sublayer does around it.
 //
-//   pe_dyt        out = dyt(stream (+ delta))                      the norm in front of a sublayer (optionally of gathered rows)
+//   pe_dyt        out = dyt(x)                                     the norm in front of a sublayer (optionally of gathered rows)
 //   pe_dyt_add    stream += dyt_1(delta) ;  out = dyt_2(stream)    the norm behind a sublayer, its add, and (optionally) the
 //                                                                  norm in front of the next sublayer, in one pass
 //   pe_rmsnorm_pair_mix   out = sa * unit(a) * wa + sb * unit(b) * wb   two outputs side by side, each divided by its own
 //                                                                  root mean square over the row
+//   pe_concat_split       rows [a | b] of two float32 matrices in the run dtype, as two terms whose sum has 16 significant bits
 #include "api.h"
 #include "common.cuh"
 
@@ -60,6 +61,22 @@ __global__ void rmsnorm_pair_mix_kernel(const T* a, const T* b, const float* __r
   const float ia = rsqrtf(ssa / (float)dim + eps) * sa, ib = rsqrtf(ssb / (float)dim + eps) * sb;
   for (int c = threadIdx.x; c < dim; c += blockDim.x)
     out[(size_t)r * dim + c] = from_f32<T>(to_f32<T>(ar[c]) * ia * wa[c] + to_f32<T>(br[c]) * ib * wb[c]);
+}
+
+// rows [a | b] of two float32 matrices side by side, as the run dtype's rounding `hi` and (bfloat16) what that left over `lo`
+template <typename T>
+__global__ void concat_split_kernel(const float* a, const float* b, T* __restrict__ hi, T* __restrict__ lo, int n_rows, int dim) {
+  pdl_wait_block();
+  pdl_launch_dependents();
+  const size_t total = (size_t)n_rows * 2 * dim;
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+    const size_t r = i / (2 * dim);
+    const int c = (int)(i - r * 2 * dim);
+    const float v = c < dim ? a[r * dim + c] : b[r * dim + (c - dim)];
+    const T h = from_f32<T>(v);
+    hi[i] = h;
+    if (lo) lo[i] = from_f32<T>(v - to_f32<T>(h));
+  }
 }
 
 static int grid_for(size_t total, int threads) {
@@ -118,6 +135,22 @@ extern "C" int pe_rmsnorm_pair_mix(int dtype, const void* a, const void* b, cons
   else if (dtype == PE_BF16)
     pe::launch(pe::rmsnorm_pair_mix_kernel<__nv_bfloat16>, n_rows, threads, 0, stream, (const __nv_bfloat16*)a,
                (const __nv_bfloat16*)b, wa, wb, eps, sa, sb, (__nv_bfloat16*)out, n_rows, dim);
+  else
+    return PE_ERR_UNSUPPORTED_DTYPE;
+  PE_LAUNCH_CHECK();
+  return PE_OK;
+}
+
+// hi = [a | b] in the run dtype; lo (may be null) = the part of [a | b] that the rounding to hi left over, rounded likewise.
+extern "C" int pe_concat_split(int dtype, const float* a, const float* b, void* hi, void* lo, int n_rows, int dim,
+                               cudaStream_t stream) {
+  if (n_rows <= 0) return PE_OK;
+  if (dim <= 0) return PE_ERR_BAD_ARGUMENT;
+  const int threads = 256, grid = pe::grid_for((size_t)n_rows * 2 * dim, threads);
+  if (dtype == PE_F32)
+    pe::launch(pe::concat_split_kernel<float>, grid, threads, 0, stream, a, b, (float*)hi, (float*)lo, n_rows, dim);
+  else if (dtype == PE_BF16)
+    pe::launch(pe::concat_split_kernel<__nv_bfloat16>, grid, threads, 0, stream, a, b, (__nv_bfloat16*)hi, (__nv_bfloat16*)lo, n_rows, dim);
   else
     return PE_ERR_UNSUPPORTED_DTYPE;
   PE_LAUNCH_CHECK();

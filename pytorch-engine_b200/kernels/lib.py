@@ -99,6 +99,7 @@ _SIGNATURES = {
     "pe_dyt": [I, I, P, P, P, P, F, P, I, I, P],
     "pe_dyt_add": [I, P, P, P, P, F, P, P, F, P, I, I, P],
     "pe_rmsnorm_pair_mix": [I, P, P, P, P, F, F, F, P, I, I, P],
+    "pe_concat_split": [I, P, P, P, P, I, I, P],
     "pe_norm_token_shift": [I, P, P, F, P, P, P, P, P, P, I, I, I, P, P],
     "pe_depth_average": [P, L, P, I, P, P, L, P],
     "pe_polynorm": [I, P, P, F, P, I, I, P],

@@ -1020,3 +1020,15 @@ def rmsnorm_pair_mix(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: tor
     check(library().pe_rmsnorm_pair_mix(dtype_tag(a.dtype), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(eps), float(sa), float(sb),
                                         _ptr(out), n, dim, _stream()), "rmsnorm_pair_mix")
     _count(1)
+
+
+def concat_split(a: torch.Tensor, b: torch.Tensor, hi: torch.Tensor, lo: Optional[torch.Tensor]) -> None:
+    """``hi = [a | b]`` (two float32 matrices side by side) in ``hi``'s dtype; ``lo``: what that rounding left over, rounded
+    likewise, so that ``hi + lo`` holds 16 significant bits of every value (csrc/dyt.cu)."""
+    n, dim = a.shape
+    _need(a.dtype == torch.float32 and b.dtype == torch.float32 and a.is_contiguous() and b.is_contiguous() and a.shape == b.shape,
+          "concat_split: two float32 matrices of one shape")
+    _need(hi.is_contiguous() and tuple(hi.shape) == (n, 2 * dim) and (lo is None or (lo.is_contiguous() and lo.shape == hi.shape
+                                                                                   and lo.dtype == hi.dtype)), "concat_split: outputs")
+    check(library().pe_concat_split(dtype_tag(hi.dtype), _ptr(a), _ptr(b), _ptr(hi), _ptr(lo), n, dim, _stream()), "concat_split")
+    _count(1)

@@ -81,8 +81,10 @@ class DepthAverage:
 @register("stream", "input_mix")
 class InputMix:
     """``x <- W [x ; x0]`` with ``x0`` the embedding's output of this step (``ctx.embedding_output``; the plan sets
-    ``keep_embedding_output``).  params: ``dim``.  weights: ``weight [dim, 2 * dim]`` (the stream's half first).  The product's
-    inputs are in the run dtype, its result is written to the float32 stream."""
+    ``keep_embedding_output``).  params: ``dim``.  weights: ``weight [dim, 2 * dim]`` (the stream's half first).  The result is
+    the new float32 stream, so its inputs are not cut to the run dtype's 8 bits: in a bfloat16 run ``[x ; x0]`` goes into the
+    product as two bfloat16 terms (its rounding, and the rounding of what that left over) stacked as rows of one product, whose
+    float32 halves are added."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
@@ -102,12 +104,18 @@ class InputMix:
         if x0 is None:
             raise ValueError("input_mix needs the embedding's output of the step (ModelPlan.keep_embedding_output)")
         n, dim = stream.shape
-        both = ctx.buffer("input_mix.both", (n, 2 * dim), rt.dtype)
-        both[:, :dim].copy_(stream)
-        both[:, dim:].copy_(x0)
-        y = rt.linear(both, self.weight, out=stream, out_dtype=torch.float32)
-        if y.data_ptr() != stream.data_ptr():
+        if rt.dtype == torch.float32:
+            both = ctx.buffer("input_mix.both", (n, 2 * dim), rt.dtype)
+            ops.concat_split(stream, x0, both, None)
+            mixed = ctx.buffer("input_mix.mixed", (n, dim), torch.float32)
+            y = rt.linear(both, self.weight, out=mixed)
             stream.copy_(y)
+            return stream
+        both = ctx.buffer("input_mix.both", (2 * n, 2 * dim), rt.dtype)
+        ops.concat_split(stream, x0, both[:n], both[n:])
+        mixed = ctx.buffer("input_mix.mixed", (2 * n, dim), torch.float32)
+        y = rt.linear(both, self.weight, out=mixed, out_dtype=torch.float32)
+        torch.add(y[:n], y[n:], out=stream)
         return stream
 
 

@@ -362,7 +362,7 @@ def random_weights(cfg: dict, seed: int, std: float = 0.08) -> Dict[str, torch.T
         mlp = spec.get("mlp")
         if mlp is not None:
             ff, E = int(mlp["expert"]["ff"]), int(mlp["router"]["experts"])
-            mat(f"{p}.mlp.router", E, W, s=1.5 * s_in)
+            mat(f"{p}.mlp.router", E, W, s=4.0 * s_in)      # decisive scores: few close calls between experts
             for e in range(E):
                 mat(f"{p}.mlp.e{e}.gate", ff, W, s=s_in)
                 mat(f"{p}.mlp.e{e}.up", ff, W, s=s_in)
