@@ -3,7 +3,7 @@
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
     python bench.py --micro gemm|gemm_mid|prefill_attention|decode_attention|rope_append|sampler   (single kernels, text)
-    python bench.py --archs [--arch-sizes w2048,w4096] [--arch-names vabelorn,qwen3,lunadra,vemepel]
+    python bench.py --archs [--arch-sizes w2048,w4096] [--arch-names vabelorn,qwen3,lunadra,vemepel,zonevik]
                                                            (these architectures beside Qwen3 at equal sizes; bench_archs.py)
 
 A step is one decode step: every live sequence gets one token (model step + sampler).  The default
@@ -179,9 +179,9 @@ def main():
     ap.add_argument("--no-cuda-graph", action="store_true")
     ap.add_argument("--no-baseline", action="store_true", help="skip the plain PyTorch model that vs_baseline divides by")
     ap.add_argument("--archs", action="store_true",
-                    help="instead: the Vabelorn, Lunadra and Vemepel architectures beside Qwen3 at equal layer sizes, models and kernel pairs (bench_archs.py)")
+                    help="instead: the Vabelorn, Lunadra, Vemepel and Zonevik architectures beside Qwen3 at equal layer sizes, models and kernel pairs (bench_archs.py)")
     ap.add_argument("--arch-sizes", type=str, default="", help="with --archs: names of the sizes to run (default: all)")
-    ap.add_argument("--arch-names", type=str, default="", help="with --archs: which of vabelorn, qwen3, lunadra, vemepel to run (default: all)")
+    ap.add_argument("--arch-names", type=str, default="", help="with --archs: which of vabelorn, qwen3, lunadra, vemepel, zonevik to run (default: all)")
     ap.add_argument("--micro", type=str, default=None,
                     help="time single kernels at the preset's sizes instead (gemm, prefill_attention, decode_attention, rope_append, sampler) and print text")
     args = ap.parse_args()

@@ -597,6 +597,156 @@ def vemepel_kernel_pairs(pe, torch, s, peaks, prompt, batch, context):
     return out
 
 
+def zonevik_config(pe, s):
+    """Zonevik at the same width, attention heads, feed-forward and vocabulary: window attention that keeps the first positions
+    beside a state-space mixer (inner width twice the model's, heads of 64, 128 state rows), the gated delta rule (its state as
+    large as Lunadra's), gated attention with scaled rotation; routed experts (8, two chosen among the two best of four groups)
+    whose chosen experts together are half as wide as the dense feed-forward; the two middle layers run twice."""
+    moe = {"kind": "moe", "router": {"experts": 8, "top": 2, "groups": {"count": 4, "keep": 2}}, "expert": {"ff": s["ff"] // 4}}
+    side = {"type": "parallel",
+            "mixer": {"left": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                               "scale": 1.0 / math.sqrt(s["dim"]), "mask": {"size": 1024, "keep_first": 4}},
+                      "right": {"heads": 2 * s["width"] // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}},
+            "mlp": moe}
+    delta = {"type": "delta", "mixer": {"heads": s["wkv_heads"] // 4, "kv_heads": s["wkv_heads"] // 8, "dim": 128, "vdim": 128, "conv": 4},
+             "mlp": moe}
+    att = {"type": "attention", "mixer": {"heads": s["heads"], "kv_heads": s["kv_heads"], "dim": s["dim"], "vdim": s["dim"],
+                                          "scale": 1.0 / math.sqrt(s["dim"]),
+                                          "rot": {"base": 1e6, "dims": s["dim"] // 2, "scaling": YARN}}, "mlp": moe}
+    layers = [side, delta, att, att][:s["layers"]] + [att] * max(0, s["layers"] - 4)
+    return pe.ZonevikConfig.from_dict({"architecture": "Zonevik", "vocab": s["vocab"], "width": s["width"], "norm": {"eps": 1e-6},
+                                       "embedding": {"scale": math.sqrt(s["width"])}, "loop": {"start": 1, "stop": 3, "times": 2},
+                                       "layers": layers})
+
+
+def zonevik_kernel_pairs(pe, torch, s, peaks, prompt, batch, context):
+    """The kernels that only Zonevik has, each beside the like kernel of the Lunadra path (the closest model: window attention
+    beside a recurrence, the gated delta rule, routed experts) at the same shape.  A kernel's roofline time is the larger of
+    its bytes over the copy bandwidth and its float32 operations over the CUDA cores' rate; ``times_as_far_from_roofline``
+    divides the new kernel's distance from its roofline by the like kernel's."""
+    ops = pe.kernels.ops
+    dev = torch.device("cuda:0")
+    bf = torch.bfloat16
+    width = s["width"]
+    hbm_gbs, BF16_TFLOPS = peaks["hbm_gbs"], peaks.get("bf16_tflops") or 1590.0
+    flush = torch.zeros(96 * 2 ** 20, device=dev)
+    status = torch.zeros(4, dtype=torch.int32, device=dev)
+    out = {}
+
+    def us_of(fn):
+        return 1e3 * timed(torch, fn, 20, 5, flush, graph=True)
+
+    def roof_us(nbytes, flops=0.0):
+        return max(nbytes / (hbm_gbs * 1e9), flops / (FP32_TFLOPS * 1e12)) * 1e6
+
+    def entry(name, us_new, roof_new, like, us_like, roof_like):
+        out[name] = {"us": round(us_new, 2), "roofline_us": round(roof_new, 2), "of_roofline": round(roof_new / us_new, 3)}
+        if like:
+            out[name].update({"like_kernel": like, "like_us": round(us_like, 2), "like_of_roofline": round(roof_like / us_like, 3),
+                              "times_as_far_from_roofline": round((us_new / roof_new) / (us_like / roof_like), 2)})
+
+    for what, n_seqs, q_len in (("prompt", 1, prompt), ("decode", batch, 1)):
+        n = n_seqs * q_len
+        qstart = torch.arange(0, n + 1, q_len, dtype=torch.int32, device=dev)
+        slots = torch.arange(n_seqs, dtype=torch.int32, device=dev)
+        chunked = q_len > 128
+        # the like kernel of the recurrence: the gated delta rule at Lunadra's shape
+        DH, DG, dd, ddv = s["wkv_heads"] // 4, s["wkv_heads"] // 8, 128, 128
+        ch = 2 * DG * dd + DH * ddv
+        qkv = (torch.randn(n, ch, device=dev) * 0.5).to(bf)
+        a_lin, beta = torch.randn(n, DH * dd, device=dev), torch.randn(n, DH, device=dev)
+        dtb, alog, nw2 = torch.zeros(DH * dd, device=dev), torch.zeros(DH, device=dev), torch.ones(ddv, device=dev)
+        gate = torch.randn(n, DH * ddv, device=dev).to(bf)
+        o2 = torch.empty(n, DH * ddv, dtype=bf, device=dev)
+        S2 = torch.zeros(n_seqs, DH, dd, ddv, device=dev)
+        dmax = -(-q_len // 128) if chunked else 1
+        scratch_d = torch.empty(ops.delta_rule_scratch_floats(n_seqs, DH, dd, ddv, dmax), device=dev) if chunked else None
+        us_delta = us_of(lambda: ops.delta_rule_recurrence(qkv, a_lin, dtb, alog, beta, gate, nw2, 1e-6, dd ** -0.5, o2, S2, slots, qstart,
+                                                           n_seqs, q_len, DH, DG, dd, ddv, status, 128 if chunked else 0, dmax, scratch_d))
+        roof_delta = roof_us(n * (ch * 2 + DH * dd * 4 + DH * ddv * 4) + n_seqs * DH * dd * ddv * 8, n * DH * dd * ddv * 7.0)
+        # the same kernel with one decay a head and the silu gate (what Zonevik's delta layers run)
+        a_head, dtb_h = torch.randn(n, DH, device=dev), torch.zeros(DH, device=dev)
+        us = us_of(lambda: ops.delta_rule_recurrence(qkv, a_head, dtb_h, alog, beta, gate, nw2, 1e-6, dd ** -0.5, o2, S2, slots, qstart,
+                                                     n_seqs, q_len, DH, DG, dd, ddv, status, 128 if chunked else 0, dmax, scratch_d,
+                                                     head_decay=True, gate_silu=True))
+        entry(f"{what}: gated delta recurrence with one decay a head, silu gate", us,
+              roof_us(n * (ch * 2 + DH * 8 + DH * ddv * 4) + n_seqs * DH * dd * ddv * 8, n * DH * dd * ddv * 7.0),
+              "delta_rule_recurrence (decay per channel)", us_delta, roof_delta)
+        # the state-space recurrence
+        H, dv, N, G = 2 * width // 64, 64, 128, 8
+        xbc = (torch.randn(n, H * dv + 2 * G * N, device=dev) * 0.5).to(bf)
+        dt = torch.randn(n, H, device=dev).to(bf)
+        dtb2, alog2, D = torch.zeros(H, device=dev), torch.zeros(H, device=dev), torch.ones(H, device=dev)
+        y = torch.empty(n, H * dv, device=dev)
+        S = torch.zeros(n_seqs, H, N, dv, device=dev)
+        smax = -(-q_len // 64) if chunked else 1
+        scratch_s = torch.empty(ops.ssd_scratch_floats(n_seqs, H, N, dv, smax), device=dev) if chunked else None
+        us = us_of(lambda: ops.ssd_recurrence(xbc, dt, dtb2, alog2, D, y, S, slots, qstart, n_seqs, q_len, H, G, N, dv, status,
+                                              64 if chunked else 0, smax, scratch_s))
+        passes = 2.0 if chunked else 1.0     # the chunked form walks every token twice (fold, then outputs)
+        entry(f"{what}: state-space recurrence", us,
+              roof_us(n * ((H * dv + 2 * G * N) * 2 + H * 2 + H * dv * 4) + n_seqs * H * N * dv * 8, n * H * N * dv * 4.0),
+              "delta_rule_recurrence", us_delta, roof_delta)
+        out[f"{what}: state-space recurrence"]["fp32_tflops"] = round(passes * n * H * N * dv * 4.0 / us / 1e6, 1)
+        # gate, then the norm over parts of the row, beside the plain norm of a row of the same size
+        z = torch.randn(n, H * dv, device=dev).to(bf)
+        nw = torch.ones(H * dv, device=dev)
+        yo = torch.empty(n, H * dv, dtype=bf, device=dev)
+        us = us_of(lambda: ops.gated_part_norm(y, z, nw, 1e-6, yo, 8))
+        us_like = us_of(lambda: ops.rmsnorm(z, nw, yo, 1e-6))
+        entry(f"{what}: silu gate, norm over parts of the row", us, roof_us(n * H * dv * 8), "rmsnorm", us_like, roof_us(n * H * dv * 4))
+        # the norms around a sublayer
+        stream = torch.randn(n, width, device=dev)
+        delta = torch.randn(n, width, device=dev).to(bf)
+        delta2 = torch.randn(n, width, device=dev).to(bf)
+        w, b0 = torch.ones(width, device=dev), torch.zeros(width, device=dev)
+        normed = torch.empty(n, width, dtype=bf, device=dev)
+        us_like = us_of(lambda: ops.rmsnorm_residual(stream, delta, w, normed, 1e-6))
+        roof_like = roof_us(n * width * (8 + 2 + 2))
+        us = us_of(lambda: ops.dyt(stream, w, b0, 0.8, normed))
+        entry(f"{what}: tanh norm of the stream", us, roof_us(n * width * 6), "rmsnorm_residual", us_like, roof_like)
+        us = us_of(lambda: ops.dyt_add(stream, delta, w, b0, 0.8, (w, b0, 0.7), normed))
+        entry(f"{what}: tanh norm of a sublayer's output, add, tanh norm of the new stream", us, roof_us(n * width * 12),
+              "rmsnorm_residual", us_like, roof_like)
+        us = us_of(lambda: ops.rmsnorm_pair_mix(delta, delta2, w, w, 1e-6, 0.5, 0.5, normed))
+        us_sum = us_of(lambda: ops.rmsnorm_residual_sum(stream, [delta, delta2], [1.0, 1.0], w, normed, 1e-6))
+        entry(f"{what}: two outputs, each over its root mean square, half their sum", us, roof_us(n * width * 6),
+              "rmsnorm_residual_sum of two", us_sum, roof_us(n * width * (8 + 4 + 2)))
+        # the router
+        E, top = 8, 2
+        logits = torch.randn(n, E, device=dev)
+        corr = torch.zeros(E, device=dev)
+        chosen = torch.empty(n, top, dtype=torch.int32, device=dev)
+        weight = torch.empty(n, top, device=dev)
+        us = us_of(lambda: ops.moe_route_sigmoid_groups(logits, top, 4, 2, chosen, weight))
+        us_like = us_of(lambda: ops.moe_route(logits, corr, top, chosen, weight))
+        entry(f"{what}: experts chosen among the best groups", us, roof_us(n * (E * 4 + top * 8)), "moe_route", us_like, roof_us(n * (E * 4 + top * 8)))
+        # window attention that keeps the first positions, beside the window attention of the Lunadra path
+        nh, nkv, d = s["heads"], s["kv_heads"], s["dim"]
+        length = context if what == "decode" else prompt
+        pages = -(-length // 64)
+        kp = (torch.randn(n_seqs * pages + 1, nkv, 64, d, device=dev) * 0.5).to(bf)
+        vp = (torch.randn(n_seqs * pages + 1, nkv, 64, d, device=dev) * 0.5).to(bf)
+        table = torch.arange(n_seqs * pages, dtype=torch.int32, device=dev).view(n_seqs, pages).contiguous()
+        past = torch.full((n_seqs,), length - q_len, dtype=torch.int32, device=dev)
+        q = (torch.randn(n, nh * d, device=dev) * 0.5).to(bf)
+        ao = torch.empty(n, nh * d, dtype=bf, device=dev)
+        decode = what == "decode"
+        sk, ms, floor = ops.attention_mma_decode_ranges(dev, d, n_seqs, nkv, length, 512) if decode else (512, 0, 0)
+        scr2 = torch.empty(ops.attention_generic_scratch_floats(n_seqs, nh, d, max(ms, 1)), device=dev) if decode else None
+        us = us_of(lambda: ops.attention_mma_masked(decode, q, ao, n_seqs, q_len, nh, nkv, d, d ** -0.5, qstart, past, slots, table,
+                                                    kp.shape[0], kp, vp, scr2, sk, ms, status, min_range_keys=floor, window=1024,
+                                                    keep_first=4))
+        us_like = us_of(lambda: ops.attention_mma(decode, q, ao, n_seqs, q_len, nh, nkv, d, d ** -0.5, 1024, qstart, past, slots, table,
+                                                  kp.shape[0], kp, vp, scr2, sk, ms, status, min_range_keys=floor))
+        keys = min(length, 1024 + 4)
+        att_bytes = n_seqs * keys * nkv * d * 4 + n * nh * d * 4 if decode else n * (nh + nkv) * d * 4
+        att_flops = 4.0 * n * nh * d * (keys if decode else min(1024, length) * 0.75)
+        roof = max(att_bytes / (hbm_gbs * 1e9), att_flops / (BF16_TFLOPS * 1e12)) * 1e6
+        entry(f"{what}: window attention with kept first positions", us, roof, "attention_mma (window)", us_like, roof)
+    return out
+
+
 def main(args):
     import torch
 
@@ -613,9 +763,9 @@ def main(args):
     for name in names:
         s = SIZES[name]
         row = {"shape": s}
-        wanted = [a for a in (args.arch_names or "vabelorn,qwen3,lunadra,vemepel").split(",") if a]
+        wanted = [a for a in (args.arch_names or "vabelorn,qwen3,lunadra,vemepel,zonevik").split(",") if a]
         for arch, make in (("vabelorn", vabelorn_config), ("qwen3", qwen3_config), ("lunadra", lunadra_config),
-                           ("vemepel", vemepel_config)):
+                           ("vemepel", vemepel_config), ("zonevik", zonevik_config)):
             if arch not in wanted:
                 continue
             row[arch] = model_speeds(pe, torch, make(pe, s), prompt, batch, context, args.steps, max(args.warmup, 3))
@@ -631,6 +781,10 @@ def main(args):
         if "vemepel" in wanted:
             row["vemepel_kernels"] = vemepel_kernel_pairs(pe, torch, s, peaks, prompt, batch, context)
             for k, v in row["vemepel_kernels"].items():
+                print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
+        if "zonevik" in wanted:
+            row["zonevik_kernels"] = zonevik_kernel_pairs(pe, torch, s, peaks, prompt, batch, context)
+            for k, v in row["zonevik_kernels"].items():
                 print(f"[{name}] {k}: {v}", file=sys.stderr, flush=True)
         result["sizes"][name] = row
     result["gpu_launches"] = pe.kernels.ops.launch_count()

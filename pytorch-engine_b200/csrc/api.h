@@ -49,7 +49,8 @@ int pe_attention_mma_ex(int decode, const void* q, long long q_ld, void* out, lo
     const int* page_table, int table_stride, int num_pages, const void* k_pages, const void* v_pages, float* scratch,
     int split_keys, int max_splits, int min_range_keys, int* status, cudaStream_t stream);
 int pe_attention_mma_masked(int decode, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs, int max_q,
-    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk, int v_heads, int out_f32, int split_p, int sink,
+    int n_heads, int n_kv_heads, int head_dim, float scale, int window, int chunk, int keep_first, int v_heads, int out_f32,
+    int split_p, int sink,
     const float* out_cos, const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past,
     const int* seq_slot, const int* page_table, int table_stride, int num_pages, const void* k_pages,
     const void* v_pages, float* scratch, int split_keys, int max_splits, int min_range_keys, int* status,

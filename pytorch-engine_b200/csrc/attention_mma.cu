@@ -55,6 +55,8 @@ struct Args {
   // split_p != 0: a probability enters the P.V product as two bfloat16 terms (its rounding, and the rounding of what
   // that left over), in two products: 16 significant bits of every weight instead of 8
   int split_p;
+  // keep_first > 0 (with a window): keys at positions < keep_first stay visible to every later query
+  int keep_first;
 };
 
 // What rounding (p0, p1) to bfloat16 left over, as a bfloat16 pair.
@@ -168,14 +170,17 @@ __global__ void __launch_bounds__(128, SPLIT_P ? 2 : 3) prefill_kernel(Args a, c
   const int first_pos = past + row0 / group, last_pos = past + last_row / group;
   const int k_begin = first_visible(a, first_pos) / BN * BN;
   const int k_end = last_pos + 1;
-  const int n_tiles = (k_end - k_begin + BN - 1) / BN;
+  // kept first keys in front of the block's window: their pages come first, then the pages from k_begin on
+  const int keep_tiles = a.keep_first > 0 ? (min(a.keep_first, k_begin) + BN - 1) / BN : 0;
+  const int n_tiles = keep_tiles + (k_end - k_begin + BN - 1) / BN;
+  auto tile_k0 = [&](int it) { return it < keep_tiles ? it * BN : k_begin + (it - keep_tiles) * BN; };
 
   // first K/V page in flight, then stage Q
   if (tid == 0) {
     tma::mbar_init(&bars[0], 1);
     tma::mbar_init(&bars[1], 1);
     tma::fence_barrier_init();
-    issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin, smem, &bars[0]);
+    issue_page<HD>(a, &kmap, &vmap, slot, kvh, tile_k0(0), smem, &bars[0]);
   }
   constexpr int CPR = HD / 8;
   for (int i = tid; i < 64 * CPR; i += 128) {
@@ -209,16 +214,16 @@ __global__ void __launch_bounds__(128, SPLIT_P ? 2 : 3) prefill_kernel(Args a, c
   float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.f, l_hi = 0.f;
 
   for (int it = 0; it < n_tiles; ++it) {
-    const int k0 = k_begin + it * BN;
+    const int k0 = tile_k0(it);
     char* stage = smem + (it & 1) * STAGE;
     // next page into the other stage (everyone left it at the end of the last round)
     if (tid == 0 && it + 1 < n_tiles)
-      issue_page<HD>(a, &kmap, &vmap, slot, kvh, k0 + BN, smem + ((it + 1) & 1) * STAGE, &bars[(it + 1) & 1]);
+      issue_page<HD>(a, &kmap, &vmap, slot, kvh, tile_k0(it + 1), smem + ((it + 1) & 1) * STAGE, &bars[(it + 1) & 1]);
     if (!tma::mbar_wait(&bars[it & 1], (it >> 1) & 1)) {
       give_up(a, bars, 2, 1);
       return;
     }
-    const bool skip = (k0 > warp_last_pos) || (k0 + BN - 1 < warp_first_lo);
+    const bool skip = (k0 > warp_last_pos) || (k0 + BN - 1 < warp_first_lo && k0 >= a.keep_first);
     if (!skip) {
       const uint32_t ks_base = smem_u32(stage), vs_base = ks_base + BN * HD * 2;
       float s[8][4];
@@ -256,7 +261,7 @@ __global__ void __launch_bounds__(128, SPLIT_P ? 2 : 3) prefill_kernel(Args a, c
           for (int e = 0; e < 4; ++e) {
             const int kpos = k0 + n * 8 + 2 * t + (e & 1);
             const int qpos = (e < 2) ? pos_lo : pos_hi;
-            const bool vis = kpos <= qpos && kpos >= ((e < 2) ? lo_lo : lo_hi);
+            const bool vis = kpos <= qpos && (kpos >= ((e < 2) ? lo_lo : lo_hi) || kpos < a.keep_first);
             const float v = vis ? s[n][e] * a.scale_log2 : -INFINITY;
             s[n][e] = v;
             if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -362,16 +367,18 @@ __global__ void __launch_bounds__(128, SPLIT_P ? 2 : 3) prefill_kernel(Args a, c
 }
 
 // One warp folds its 16 keys (key0 .. key0+15 of the page that starts at position k0) into the
-// running softmax state of the group's rows.  Keys outside [k_first, k_hi) are masked.
+// running softmax state of the group's rows.  Keys outside [k_first, k_hi) and keys inside [hole_lo, hole_hi) (what lies
+// between the kept first keys and the window) are masked.
 template <int HD, bool SPLIT_P>
 __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_base, int key0, int k0, int k_first,
-                                                 int k_hi, float scale_log2, const uint32_t (&qf)[HD / 16][4],
+                                                 int k_hi, int hole_lo, int hole_hi, float scale_log2,
+                                                 const uint32_t (&qf)[HD / 16][4],
                                                  float (&o)[HD / 8][4], float& m_lo, float& m_hi, float& l_lo,
                                                  float& l_hi, int lane) {
   constexpr int KS = HD / 16;
   constexpr int NO = HD / 8;
   const int t = lane & 3;
-    if (k0 + key0 < k_hi && k0 + key0 + 15 >= k_first) {
+    if (k0 + key0 < k_hi && k0 + key0 + 15 >= k_first && !(k0 + key0 >= hole_lo && k0 + key0 + 15 < hole_hi)) {
   float s[2][4];
   s[0][0] = s[0][1] = s[0][2] = s[0][3] = s[1][0] = s[1][1] = s[1][2] = s[1][3] = 0.f;
 #pragma unroll
@@ -388,7 +395,7 @@ __device__ __forceinline__ void decode_fold_page(uint32_t ks_base, uint32_t vs_b
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
       const int kpos = k0 + key0 + n * 8 + 2 * t + (e & 1);
-      const bool vis = kpos >= k_first && kpos < k_hi;
+      const bool vis = kpos >= k_first && kpos < k_hi && !(kpos >= hole_lo && kpos < hole_hi);
       const float v = vis ? s[n][e] * scale_log2 : -INFINITY;
       s[n][e] = v;
       if (e < 2) mx_lo = fmaxf(mx_lo, v); else mx_hi = fmaxf(mx_hi, v);
@@ -477,11 +484,19 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
   const int k_lo = split * per_range, k_hi = min(len, k_lo + per_range);
   if (k_lo >= len) return;
   const int win_lo = first_visible(a, len - 1);
-  if (k_hi <= win_lo) return;
+  const int keep = a.keep_first > 0 ? min(a.keep_first, win_lo) : 0;   // kept first keys in front of the window
+  if (k_hi <= win_lo && k_lo >= keep) return;
   const int slot = a.seq_slot[b];
-  const int k_first = max(k_lo, win_lo);         // first visible key of this range
-  const int k_begin = k_first / BN * BN;
-  const int n_tiles = (k_hi - k_begin + BN - 1) / BN;
+  const int k_first = k_lo < keep ? k_lo : max(k_lo, win_lo);          // first visible key of this range
+  // the range's pages: those that hold kept keys (from k_lo on, which is a page's start), then those from the window's
+  // first key on; a page that holds both is taken once, with the second lot
+  const int k_begin = max(k_lo, win_lo) / BN * BN;
+  const int win_tiles = k_hi > win_lo ? (k_hi - k_begin + BN - 1) / BN : 0;
+  int keep_tiles = k_lo < keep ? (min(keep, k_hi) - k_lo + BN - 1) / BN : 0;
+  if (win_tiles > 0 && k_lo + keep_tiles * BN > k_begin) keep_tiles = (k_begin - k_lo) / BN;
+  const int n_tiles = keep_tiles + win_tiles;
+  auto tile_k0 = [&](int it) { return it < keep_tiles ? k_lo + it * BN : k_begin + (it - keep_tiles) * BN; };
+  const int hole_lo = keep, hole_hi = keep > 0 ? win_lo : 0;
   const int last_page_k0 = (len - 1) / BN * BN;
   if (tid == 0) {
 #pragma unroll
@@ -489,15 +504,15 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
     tma::fence_barrier_init();
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
-      if (s < n_tiles && k_begin + s * BN != last_page_k0)
-        issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
+      if (s < n_tiles && tile_k0(s) != last_page_k0)
+        issue_page<HD>(a, &kmap, &vmap, slot, kvh, tile_k0(s), smem + s * STAGE, &bars[s]);
   }
   pdl_wait_block();
   if (tid == 0) {
 #pragma unroll
     for (int s = 0; s < STAGES - 1; ++s)
-      if (s < n_tiles && k_begin + s * BN == last_page_k0)
-        issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + s * BN, smem + s * STAGE, &bars[s]);
+      if (s < n_tiles && tile_k0(s) == last_page_k0)
+        issue_page<HD>(a, &kmap, &vmap, slot, kvh, tile_k0(s), smem + s * STAGE, &bars[s]);
   }
   constexpr int CPR = HD / 8;
   for (int i = tid; i < 16 * CPR; i += 128) {
@@ -522,14 +537,14 @@ __global__ void __launch_bounds__(128) decode_split_kernel(Args a, const __grid_
     // keep STAGES-1 pages in flight (the stage refilled here was released by the last round's barrier)
     const int nxt = it + STAGES - 1;
     if (tid == 0 && nxt < n_tiles)
-      issue_page<HD>(a, &kmap, &vmap, slot, kvh, k_begin + nxt * BN, smem + (nxt % STAGES) * STAGE, &bars[nxt % STAGES]);
+      issue_page<HD>(a, &kmap, &vmap, slot, kvh, tile_k0(nxt), smem + (nxt % STAGES) * STAGE, &bars[nxt % STAGES]);
     if (!tma::mbar_wait(&bars[it % STAGES], (it / STAGES) & 1)) {
       give_up(a, bars, STAGES, 2);
       return;
     }
-    const int k0 = k_begin + it * BN;
+    const int k0 = tile_k0(it);
     decode_fold_page<HD, SPLIT_P>(smem_u32(smem + (it % STAGES) * STAGE), smem_u32(smem + (it % STAGES) * STAGE) + BN * HD * 2,
-                         warp * 16, k0, k_first, k_hi, a.scale_log2, qf, o, m_lo, m_hi, l_lo, l_hi, lane);
+                         warp * 16, k0, k_first, k_hi, hole_lo, hole_hi, a.scale_log2, qf, o, m_lo, m_hi, l_lo, l_hi, lane);
     __syncthreads();
   }
   pdl_launch_dependents();
@@ -588,6 +603,9 @@ __global__ void decode_merge_kernel(Args a) {
   }
   const int win_lo = first_visible(a, len - 1);
   const int first = min(win_lo / per_range, n_splits);
+  // ranges in front of the window that hold kept first keys were computed too: [0, kept_ranges)
+  const int keep = a.keep_first > 0 ? min(a.keep_first, win_lo) : 0;
+  const int kept_ranges = min((keep + per_range - 1) / per_range, first);
   const size_t base = ((size_t)b * a.n_heads + h) * a.max_splits;
   __nv_bfloat16* o = a.out + (size_t)tq * a.out_ld + (size_t)h * HD;
   // Ranges are taken eight at a time: all their loads are issued before the first is used (this kernel
@@ -597,11 +615,12 @@ __global__ void decode_merge_kernel(Args a) {
   for (int c = threadIdx.x; c < HD; c += blockDim.x) {
     // with a sink the fold starts from one more range whose log-sum is 0 and whose output is 0
     float mx = a.sink ? 0.f : -INFINITY, denom = a.sink ? 1.f : 0.f, v = 0.f;
-    for (int s0 = first; s0 < n_splits; s0 += G) {
+    for (int lot = kept_ranges > 0 ? 0 : 1; lot < 2; ++lot)
+    for (int s0 = lot ? first : 0, s_end = lot ? n_splits : kept_ranges; s0 < s_end; s0 += G) {
       float e[G], acc[G];
 #pragma unroll
       for (int i = 0; i < G; ++i) {
-        const bool live = s0 + i < n_splits;
+        const bool live = s0 + i < s_end;
         e[i] = live ? a.part_lse[base + s0 + i] : -INFINITY;
         acc[i] = live ? a.part_acc[(base + s0 + i) * HD + c] : 0.f;
       }
@@ -734,17 +753,18 @@ extern "C" int pe_attention_mma_ex(int decode, const void* q, long long q_ld, vo
                                    int num_pages, const void* k_pages, const void* v_pages, float* scratch,
                                    int split_keys, int max_splits, int min_range_keys, int* status, cudaStream_t stream) {
   return pe_attention_mma_masked(decode, q, q_ld, out, out_ld, n_seqs, max_q, n_heads, n_kv_heads, head_dim, scale, window,
-                                 0, n_kv_heads, 0, 0, sink, out_cos, out_sin, out_rows, seq_qstart, seq_past, seq_slot,
+                                 0, 0, n_kv_heads, 0, 0, sink, out_cos, out_sin, out_rows, seq_qstart, seq_past, seq_slot,
                                  page_table, table_stride, num_pages, k_pages, v_pages, scratch, split_keys, max_splits,
                                  min_range_keys, status, stream);
 }
 
-// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), `v_heads` value
+// The same with a chunk mask (`chunk` > 0: keys inside the query's own block of that many positions), kept first keys
+// (`keep_first` > 0 with a window: positions below it stay visible however far back they lie), `v_heads` value
 // heads a page (kv head g reads value head g % v_heads), optionally a float32 output (`out_f32`: out_ld counts floats)
 // and optionally (`split_p`) every probability as two bfloat16 terms in the P.V product.
 extern "C" int pe_attention_mma_masked(int decode, const void* q, long long q_ld, void* out, long long out_ld, int n_seqs,
                                        int max_q, int n_heads, int n_kv_heads, int head_dim, float scale, int window,
-                                       int chunk, int v_heads, int out_f32, int split_p, int sink, const float* out_cos,
+                                       int chunk, int keep_first, int v_heads, int out_f32, int split_p, int sink, const float* out_cos,
                                        const float* out_sin, int out_rows, const int* seq_qstart, const int* seq_past,
                                        const int* seq_slot, const int* page_table, int table_stride, int num_pages,
                                        const void* k_pages, const void* v_pages, float* scratch, int split_keys,
@@ -752,6 +772,7 @@ extern "C" int pe_attention_mma_masked(int decode, const void* q, long long q_ld
   if (n_seqs <= 0) return PE_OK;
   if ((out_cos == nullptr) != (out_sin == nullptr)) return PE_ERR_BAD_ARGUMENT;
   if (chunk < 0 || v_heads <= 0 || (out_f32 && out_cos)) return PE_ERR_BAD_ARGUMENT;
+  if (keep_first < 0 || (keep_first > 0 && chunk > 0)) return PE_ERR_BAD_ARGUMENT;
   if (!pe_attention_mma_supported(head_dim, n_heads, n_kv_heads)) return PE_ERR_UNSUPPORTED_SIZE;
   // 16-byte vector loads of q rows; 4-byte (bfloat16 pairs) or 8-byte (float pairs) stores of output rows
   const int out_bytes = out_f32 ? 4 : 2;
@@ -768,6 +789,7 @@ extern "C" int pe_attention_mma_masked(int decode, const void* q, long long q_ld
   a.part_acc = nullptr; a.part_lse = nullptr; a.split_keys = 0; a.max_splits = 0; a.min_range_keys = 0;
   a.sink = sink; a.out_cos = out_cos; a.out_sin = out_sin; a.out_rows = out_rows;
   a.chunk = chunk; a.v_heads = v_heads; a.out_f32 = out_f32; a.split_p = split_p;
+  a.keep_first = window > 0 ? keep_first : 0;
   if (decode) {
     if (!scratch || split_keys < 0 || split_keys % pe::fa::BN || max_splits <= 0) return PE_ERR_BAD_ARGUMENT;
     if (min_range_keys < 0 || min_range_keys % pe::fa::BN) return PE_ERR_BAD_ARGUMENT;

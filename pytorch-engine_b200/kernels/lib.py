@@ -72,7 +72,7 @@ _SIGNATURES = {
     "pe_attention_generic_ex": [I, I, P, L, P, L, I, I, I, I, I, I, F, I, I, P, P, I, I, I, P, P, P, P, I, I, P, P, P,
                                 I, I, P, P],
     "pe_attention_mma_ex": [I, P, L, P, L, I, I, I, I, I, F, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I, P, P],
-    "pe_attention_mma_masked": [I, P, L, P, L, I, I, I, I, I, F, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I,
+    "pe_attention_mma_masked": [I, P, L, P, L, I, I, I, I, I, F, I, I, I, I, I, I, I, P, P, I, P, P, P, P, I, I, P, P, P, I, I, I,
                                 P, P],
     "pe_attention_latent_supported": [I, I],
     "pe_attention_latent": [I, P, L, P, L, I, I, I, I, I, F, P, P, P, P, I, I, P, P, I, I, I, P, P],

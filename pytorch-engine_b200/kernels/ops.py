@@ -320,9 +320,10 @@ def attention_mma_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seq
                          seq_slot: torch.Tensor, page_table: torch.Tensor, num_pages: int, k_pages: torch.Tensor,
                          v_pages: torch.Tensor, scratch: Optional[torch.Tensor], split_keys: int, max_splits: int,
                          status: torch.Tensor, min_range_keys: int = 0, window: int = 0, chunk: int = 0,
-                         v_heads: Optional[int] = None, split_p: bool = False) -> None:
+                         v_heads: Optional[int] = None, split_p: bool = False, keep_first: int = 0) -> None:
     """``attention_mma`` with a chunk mask (``chunk`` > 0: a query sees the keys of its own block of that many positions,
-    blocks counted from position 0), ``v_heads`` value heads in ``v_pages`` (kv head g reads value head g % v_heads: several
+    blocks counted from position 0), kept first keys (``keep_first`` > 0 with a ``window``: positions below it stay visible to
+    every later query), ``v_heads`` value heads in ``v_pages`` (kv head g reads value head g % v_heads: several
     key maps over one set of values), an output of bfloat16 or float32 (by ``out``'s dtype) and, with ``split_p``, every
     softmax weight as two bfloat16 terms in the product with the values (16 significant bits instead of 8)."""
     _need(q.stride(-1) == 1 and out.stride(-1) == 1, "attention: rows must be contiguous")
@@ -330,7 +331,7 @@ def attention_mma_masked(decode: bool, q: torch.Tensor, out: torch.Tensor, n_seq
     _need(out.dtype in (torch.bfloat16, torch.float32), "attention_mma: out bfloat16 or float32")
     check(library().pe_attention_mma_masked(
         1 if decode else 0, _ptr(q), q.stride(0), _ptr(out), out.stride(0), n_seqs, max_q, n_heads, n_kv_heads, head_dim,
-        float(scale), int(window), int(chunk), int(n_kv_heads if v_heads is None else v_heads),
+        float(scale), int(window), int(chunk), int(keep_first), int(n_kv_heads if v_heads is None else v_heads),
         1 if out.dtype == torch.float32 else 0, 1 if split_p else 0, 0, None, None, 0, _ptr(seq_qstart), _ptr(seq_past), _ptr(seq_slot),
         _ptr(page_table), page_table.shape[1], num_pages, _ptr(k_pages), _ptr(v_pages), _ptr(scratch), split_keys, max_splits,
         int(min_range_keys), _ptr(status), _stream()), "attention_mma_masked")

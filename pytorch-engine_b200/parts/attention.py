@@ -91,6 +91,8 @@ class GQAttention:
         self.scale = float(scale) if scale is not None else 1.0 / math.sqrt(self.head_dim)
         self.window = int(params["window"]) if params.get("window") else 0
         self.keep_first = int(params.get("keep_first") or 0) if self.window else 0
+        if self.keep_first and (self.sink or params.get("value_position") is not None):
+            raise ValueError("keep_first is not built together with a sink or turned values")
         self.output_gate = params.get("output_gate")
         if self.output_gate not in (None, "sigmoid"):
             raise ValueError(f"output_gate {self.output_gate!r} is not built (None or 'sigmoid')")
@@ -140,12 +142,12 @@ class GQAttention:
         # (with a sink or turned values too, if keys and values have one size and the values turn in interleaved pairs
         # over the whole head: these kernels take both in their epilogues)
         vp = self.value_position
-        fast_ok = self.v_dim == self.head_dim and not self.keep_first and (
-            vp is None or (getattr(vp, "interleaved", False) and vp.tables()[2] == self.v_dim))
+        fast_ok = self.v_dim == self.head_dim and (vp is None or (getattr(vp, "interleaved", False)
+                                                                  and vp.tables()[2] == self.v_dim))
         self.use_mma = (fast_ok and runtime.is_cuda
                         and ops.attention_mma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
         # prefill on tcgen05 where that kernel takes the shape (bfloat16, head size 128, groups up to 32)
-        self.use_umma_prefill = (fast_ok and runtime.is_cuda
+        self.use_umma_prefill = (fast_ok and runtime.is_cuda and not self.keep_first
                                  and ops.attention_umma_supported(runtime.dtype, self.head_dim, self.n_heads, self.n_kv_heads))
         self.generic_attention = bool(getattr(runtime, "generic_attention", False))   # comparisons: the general kernels only
 
@@ -224,6 +226,11 @@ class GQAttention:
                 scratch = ctx.buffer(
                     "attn.scratch",
                     (ops.attention_generic_scratch_floats(ctx.n_seqs, self.n_heads, self.head_dim, max_splits),), torch.float32)
+            if self.keep_first:        # (not with a sink or turned values: the constructor refuses that pair)
+                ops.attention_mma_masked(ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim,
+                                         self.scale, *where, scratch, split_keys, max_splits, self.runtime.status,
+                                         min_range_keys=floor, window=self.window, keep_first=self.keep_first)
+                return
             ops.attention_mma(ctx.decode, q, out, ctx.n_seqs, ctx.max_q, self.n_heads, self.n_kv_heads, self.head_dim,
                               self.scale, self.window, *where, scratch, split_keys, max_splits, self.runtime.status,
                               min_range_keys=floor, **extra)

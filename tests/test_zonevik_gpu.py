@@ -225,17 +225,19 @@ class Pages:
         self.v[page, :, pos % 64] = v
 
 
+@pytest.mark.parametrize("kernel", ["float32 arithmetic", "tensor cores"])
 @pytest.mark.parametrize("decode", [False, True])
-@pytest.mark.parametrize("window,keep", [(37, 3), (64, 64), (20, 70), (130, 1), (50, 0)])
-def test_keys_at_the_edges_of_the_window_and_of_the_kept_positions(pe, decode, window, keep):
+@pytest.mark.parametrize("window,keep", [(37, 3), (64, 64), (20, 70), (130, 1), (50, 0), (100, 129)])
+def test_keys_at_the_edges_of_the_window_and_of_the_kept_positions(pe, decode, window, keep, kernel):
     """One key matches the query far better than all others.  At the window's oldest position, or at the last kept position,
     the output is its value; one position further back (or one behind the kept ones and in front of the window) it must not
     be seen, and the output is the average of the values that are (all of score zero).  The query sits so that the edges fall
     before, on and behind page borders; a prompt's rows are checked as a whole step of several queries."""
     ops = pe.kernels.ops
-    nh, nkv, d, dv = 6, 2, 16, 24
+    nh, nkv, d, dv = (6, 2, 16, 24) if kernel == "float32 arithmetic" else (8, 2, 64, 64)
+    dt = torch.float32 if kernel == "float32 arithmetic" else torch.bfloat16
     g = torch.Generator().manual_seed(window)
-    for n in (window + 1, 128, 129, 300):
+    for n in (window + 1, 128, 129, 300, 700):
         i = n - 1                                   # the last query's position
         lo = max(0, i - window + 1)
         spots = {lo: True, lo - 1: lo - 1 < keep, keep - 1: True, keep: keep >= lo, 0: keep > 0 or lo == 0}
@@ -254,19 +256,31 @@ def test_keys_at_the_edges_of_the_window_and_of_the_kept_positions(pe, decode, w
             qstart = torch.tensor([0, nq], dtype=torch.int32, device=DEV)
             past = torch.tensor([n - nq], dtype=torch.int32, device=DEV)
             slots = torch.zeros(1, dtype=torch.int32, device=DEV)
-            out = torch.full((nq, nh * dv), float("nan"), device=DEV)
+            out = torch.full((nq, nh * dv), float("nan"), dtype=dt, device=DEV)
             status = torch.zeros(4, dtype=torch.int32, device=DEV)
             max_splits = -(-n // 64) if decode else 0
-            scratch = torch.full((ops.attention_generic_scratch_floats(1, nh, dv, max_splits),), float("nan"), device=DEV) if decode else None
-            ops.attention_generic_masked(decode, q.to(DEV), out, 1, nq, nh, nkv, d, dv, 1.0, qstart, past, slots, pages.table.to(DEV),
-                                         pages.n_pages, pages.k.to(DEV), pages.v.to(DEV), scratch, 64, max_splits, status,
-                                         window=window, keep_first=keep)
+            scratch = torch.full((ops.attention_generic_scratch_floats(1, nh, dv, max(max_splits, 3)),), float("nan"), device=DEV) if decode else None
+            where = (qstart, past, slots, pages.table.to(DEV), pages.n_pages, pages.k.to(DEV, dt), pages.v.to(DEV, dt))
+            if kernel == "float32 arithmetic":
+                ops.attention_generic_masked(decode, q.to(DEV), out, 1, nq, nh, nkv, d, dv, 1.0, *where, scratch, 64, max_splits,
+                                             status, window=window, keep_first=keep)
+            else:
+                for split_keys, splits in ((64, max_splits), (0, 3)):       # ranges of a page; three even ranges
+                    out.fill_(float("nan"))
+                    ops.attention_mma_masked(decode, q.to(DEV, dt), out, 1, nq, nh, nkv, d, 1.0, *where, scratch, split_keys, splits,
+                                             status, window=window, keep_first=keep)
+                    if not decode:
+                        break
+                    if split_keys:
+                        first = out.clone()
+                if decode:
+                    assert (out.float() - first.float()).abs().max() < 2e-2
             assert status.tolist()[0] == 0
             visible = [j for j in range(i + 1) if i - j < window or j < keep]
             assert (target in visible) == seen
             want = vals[target] if seen else vals[visible].mean(0)
             want = want.repeat_interleave(nh // nkv, dim=0).view(1, nh * dv)
-            assert (out[-1:].cpu() - want).abs().max() < 1e-3, (decode, window, keep, n, target, seen)
+            assert (out[-1:].float().cpu() - want).abs().max() < (1e-3 if dt == torch.float32 else 3e-2), (decode, window, keep, n, target, seen)
 
 
 @pytest.mark.parametrize("n_state,dv", [(8, 8), (24, 20), (64, 48), (128, 64), (136, 12), (40, 100)])
