@@ -708,10 +708,10 @@ def zonevik_kernel_pairs(pe, torch, s, peaks, prompt, batch, context):
         us = us_of(lambda: ops.dyt_add(stream, delta, w, b0, 0.8, (w, b0, 0.7), normed))
         entry(f"{what}: tanh norm of a sublayer's output, add, tanh norm of the new stream", us, roof_us(n * width * 12),
               "rmsnorm_residual", us_like, roof_like)
-        us = us_of(lambda: ops.rmsnorm_pair_mix(delta, delta2, w, w, 1e-6, 0.5, 0.5, normed))
+        us = us_of(lambda: ops.rmsnorm_pair_mix_dyt_add(delta, delta2, w, w, 1e-6, 0.5, 0.5, stream, (w, b0, 0.8), (w, b0, 0.7), normed))
         us_sum = us_of(lambda: ops.rmsnorm_residual_sum(stream, [delta, delta2], [1.0, 1.0], w, normed, 1e-6))
-        entry(f"{what}: two outputs, each over its root mean square, half their sum", us, roof_us(n * width * 6),
-              "rmsnorm_residual_sum of two", us_sum, roof_us(n * width * (8 + 4 + 2)))
+        entry(f"{what}: two outputs over their root mean squares, half their sum, tanh norm, add, next tanh norm", us,
+              roof_us(n * width * (8 + 4 + 2)), "rmsnorm_residual_sum of two", us_sum, roof_us(n * width * (8 + 4 + 2)))
         # the router
         E, top = 8, 2
         logits = torch.randn(n, E, device=dev)

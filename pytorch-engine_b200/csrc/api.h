@@ -198,7 +198,8 @@ int pe_short_conv_silu(int dtype, const void* x, long long ld, int col0, const f
 int pe_delta_rule_recurrence(int dtype, const void* qkv, const float* a, const float* dt_bias, const float* A_log,
     const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps, float q_scale, void* out, float* S,
     const int* seq_slot, const int* seq_qstart, int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots,
-    int chunk, int max_chunks, float* scratch, int head_decay, int gate_silu, int* status, cudaStream_t stream);
+    int chunk, int max_chunks, float* scratch, int head_decay, int gate_silu, long long a_ld, long long b_ld, int* status,
+    cudaStream_t stream);
 long long pe_delta_rule_scratch_floats(int n_seqs, int heads, int d, int dv, int max_chunks);
 
 // moe.cu
@@ -237,6 +238,9 @@ int pe_dyt_add(int dtype, float* stream_rows, const void* delta, const float* w1
 int pe_rmsnorm_pair_mix(int dtype, const void* a, const void* b, const float* wa, const float* wb, float eps, float sa,
     float sb, void* out, int n_rows, int dim, cudaStream_t stream);
 
+int pe_rmsnorm_pair_mix_dyt_add(int dtype, const void* a, const void* b, const float* wa, const float* wb, float eps, float sa,
+    float sb, float* stream_rows, const float* w1, const float* b1, float alpha1, const float* w2, const float* b2, float alpha2,
+    void* out, int n_rows, int dim, cudaStream_t stream);
 int pe_concat_split(int dtype, const float* a, const float* b, void* hi, void* lo, int n_rows, int dim, cudaStream_t stream);
 
 // wait_probe.cu

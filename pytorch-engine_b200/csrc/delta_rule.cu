@@ -158,6 +158,7 @@ struct DeltaArgs {
   int* status;
   int head_decay;           // != 0: one decay per head and token instead of one per key channel
   int gate_silu;            // != 0: the output gate is silu(gate) instead of sigmoid(gate)
+  long long a_ld, b_ld;     // floats between two tokens' rows of a and of b
 };
 
 __host__ __device__ inline size_t delta_unit(int d, int dv) { return (size_t)d * dv + (size_t)d * d; }
@@ -271,8 +272,8 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
     // the decays: exp(-exp(A) softplus(a + dt)) per token and key channel
     for (int e = threadIdx.x; e < nb * d; e += blockDim.x) {
       const int tt = e / d, i = e - tt * d;
-      const float z = a.head_decay ? a.a[(size_t)(tb + tt) * a.heads + head] + a.dt_bias[head]
-                                   : a.a[(size_t)(tb + tt) * a.heads * d + head * d + i] + a.dt_bias[head * d + i];
+      const float z = a.head_decay ? a.a[(size_t)(tb + tt) * a.a_ld + head] + a.dt_bias[head]
+                                   : a.a[(size_t)(tb + tt) * a.a_ld + head * d + i] + a.dt_bias[head * d + i];
       const float softplus = z > 20.f ? z : log1pf(expf(z));
       db[(size_t)tt * dpad + i] = expf(-rate * softplus);
     }
@@ -280,7 +281,7 @@ __global__ void __launch_bounds__(DREG == 0 ? 1024 : 512) delta_rule_kernel(Delt
       stage_rows_raw<T>(vb, x + (size_t)tb * channels + v_col + head * dv, channels, nb, dv, vec_v);
       if (MODE != 1) stage_rows_raw<T>(gb, (const T*)a.gate + (size_t)tb * a.gate_ld + head * dv, a.gate_ld, nb, dv, vec_g);
     }
-    if (threadIdx.x < nb) s_beta[threadIdx.x] = 1.f / (1.f + expf(-a.b[(size_t)(tb + threadIdx.x) * a.heads + head]));
+    if (threadIdx.x < nb) s_beta[threadIdx.x] = 1.f / (1.f + expf(-a.b[(size_t)(tb + threadIdx.x) * a.b_ld + head]));
     __syncthreads();
     for (int tt = warp; tt < nb; tt += n_warps) {  // a warp per token: the lengths of k and q
       float k2 = 0.f, q2 = 0.f;
@@ -583,14 +584,15 @@ extern "C" int pe_delta_rule_recurrence(int dtype, const void* qkv, const float*
                                         const float* b, const void* gate, long long gate_ld, const float* norm_w, float eps,
                                         float q_scale, void* out, float* S, const int* seq_slot, const int* seq_qstart,
                                         int n_seqs, int max_q, int heads, int kv_heads, int d, int dv, int n_slots, int chunk,
-                                        int max_chunks, float* scratch, int head_decay, int gate_silu, int* status,
-                                        cudaStream_t stream) {
+                                        int max_chunks, float* scratch, int head_decay, int gate_silu, long long a_ld,
+                                        long long b_ld, int* status, cudaStream_t stream) {
   if (n_seqs <= 0) return PE_OK;
   if (heads <= 0 || kv_heads <= 0 || heads % kv_heads || d <= 0 || dv <= 0) return PE_ERR_BAD_ARGUMENT;
   if (dv > 1024 || d > 1024) return PE_ERR_UNSUPPORTED_SIZE;
   if (dtype != PE_F32 && dtype != PE_BF16) return PE_ERR_UNSUPPORTED_DTYPE;
   pe::DeltaArgs args{qkv, a, dt_bias, A_log, b, gate, gate_ld, norm_w, eps, q_scale, out, S, seq_slot, seq_qstart,
-                     n_seqs, heads, kv_heads, d, dv, n_slots, 0, 1, nullptr, status, head_decay, gate_silu};
+                     n_seqs, heads, kv_heads, d, dv, n_slots, 0, 1, nullptr, status, head_decay, gate_silu,
+                     a_ld > 0 ? a_ld : (long long)(head_decay ? heads : heads * d), b_ld > 0 ? b_ld : (long long)heads};
   if (chunk > 0) {
     if (!scratch || max_chunks <= 0 || (long long)max_chunks * chunk < max_q || max_chunks > 32767) return PE_ERR_BAD_ARGUMENT;
     args.chunk = chunk; args.max_chunks = max_chunks; args.scratch = scratch;

@@ -5,8 +5,8 @@
 //          S <- a S + dt B x^T   (S: [n, dv]) ;  y = S^T C + D x                         head h reads group h / (heads / groups)
 //   norm   v = y * silu(z) ;  out = v / sqrt(mean_part(v^2) + eps) * w                   each of `parts` equal parts of a row
 //
-// A block owns one head's S of one sequence and walks the sequence's tokens of this step in order; thread j owns column
-// j of S (in registers up to 128 rows, in shared memory beyond).  State, dt, the decay and y are float32 whatever the
+// A block owns one head's S of one sequence and walks the sequence's tokens of this step in order; one, two or four threads
+// own a column of S (in registers up to 256 rows, in shared memory beyond).  State, dt, the decay and y are float32 whatever the
 // run dtype.  For long prompts the tokens are cut into chunks that run side by side: the update is linear in S with a
 // scalar factor, so a chunk is first folded from an empty state (MODE 1, which also leaves the sum of its log decays),
 // a small kernel chains the chunks' true start states  S_start[c+1] = exp(sum_c) S_start[c] + S_chunk[c],  and the
@@ -33,16 +33,20 @@ constexpr int kSsdBatch = 32;
 
 // MODE 0: the whole step from the slot's state; MODE 1: chunk blockIdx.z from an empty state, no outputs; MODE 3: chunk
 // blockIdx.z from its true start, outputs, and the sequence's last chunk writes the state back.
-template <typename T, int MODE, int NREG>
-__global__ void __launch_bounds__(NREG == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
+// NR > 0: a thread keeps NR rows of its column in registers and SPLIT threads share a column (lanes l, l ^ 16 for two,
+// l, l ^ 8, l ^ 16, l ^ 24 for four: a quarter of a warp reads one address of the staged B and C rows, and the partial
+// outputs meet in shuffles); more threads a column hide the walk's latencies and fill the state's loads.  NR == 0: the state
+// lives in shared memory, one thread a column.
+template <typename T, int MODE, int NR, int SPLIT>
+__global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
   extern __shared__ __align__(16) float sm[];
   __shared__ float s_dt[kSsdBatch], s_a[kSsdBatch], s_log[kSsdBatch];
   const int n = a.n, dv = a.dv, head = blockIdx.x, b = blockIdx.y, c = blockIdx.z;
   const int g = head / (a.heads / a.groups);
-  constexpr int NP = NREG > 0 ? NREG : 1;
-  const int npad = NREG > 0 ? NREG : n;
-  float* Ssm = sm;                                             // [n][dv] (NREG == 0 only)
-  float* Bb = Ssm + (NREG > 0 ? 0 : (size_t)n * dv);           // [batch][npad]
+  constexpr int NP = NR > 0 ? NR : 1;
+  const int npad = NR > 0 ? NR * SPLIT : n;
+  float* Ssm = sm;                                             // [n][dv] (NR == 0 only)
+  float* Bb = Ssm + (NR > 0 ? 0 : (size_t)n * dv);             // [batch][npad]
   float* Cb = Bb + (size_t)kSsdBatch * npad;                   // [batch][npad]
   float* xb = Cb + (size_t)kSsdBatch * npad;                   // [batch][dv]
   pdl_wait_block();
@@ -65,11 +69,14 @@ __global__ void __launch_bounds__(NREG == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) 
   float* cs = MODE != 0 ? a.scratch + cidx * unit : nullptr;
   float* gS = a.S + ((size_t)slot * a.heads + head) * unit;
   const float* src = MODE == 0 ? gS : cs;
-  const int j = threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  // the thread's column and the first of its rows
+  const int j = SPLIT == 1 ? (int)threadIdx.x : (int)(threadIdx.x >> 5) * (32 / SPLIT) + (lane & (32 / SPLIT - 1));
+  const int i0 = SPLIT == 1 ? 0 : (lane / (32 / SPLIT)) * NP;
   float Sr[NP];
-  if (NREG > 0) {
+  if (NR > 0) {
 #pragma unroll
-    for (int i = 0; i < NP; ++i) Sr[i] = (MODE != 1 && i < n && j < dv) ? src[(size_t)i * dv + j] : 0.f;
+    for (int i = 0; i < NP; ++i) Sr[i] = (MODE != 1 && i0 + i < n && j < dv) ? src[(size_t)(i0 + i) * dv + j] : 0.f;
   } else {
     for (int i = threadIdx.x; i < n * dv; i += blockDim.x) Ssm[i] = MODE == 1 ? 0.f : src[i];
   }
@@ -82,7 +89,7 @@ __global__ void __launch_bounds__(NREG == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) 
   const T* x = (const T*)a.xbc;
   const int b_col = a.heads * dv + g * n, c_col = a.heads * dv + a.groups * n + g * n, x_col = head * dv;
   const float rate = expf(a.A_log[head]), bias = a.dt_bias[head], Dh = a.D[head];
-  const bool sm_ok = NREG > 0 || (n * dv) % 4 == 0;   // the staged rows start on 16-byte boundaries
+  const bool sm_ok = NR > 0 || (n * dv) % 4 == 0;   // the staged rows start on 16-byte boundaries
   const bool vec_b = sm_ok && npad % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + b_col, a.xbc_ld, n);
   const bool vec_c = sm_ok && npad % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + c_col, a.xbc_ld, n);
   const bool vec_x = sm_ok && dv % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + x_col, a.xbc_ld, dv);
@@ -103,49 +110,62 @@ __global__ void __launch_bounds__(NREG == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) 
     __syncthreads();
     if (MODE == 1)
       for (int tt = 0; tt < nb; ++tt) log_sum += s_log[tt];
-    if (j < dv) {
+    if (NR > 0) {
+      // whole warps walk together (the parts of a column meet in shuffles); a column beyond the matrix carries zeros
+      for (int tt = 0; tt < nb; ++tt) {
+        const float decay = s_a[tt];
+        const float xj = j < dv ? xb[(size_t)tt * dv + j] : 0.f;
+        const float dx = s_dt[tt] * xj;
+        const float* Bs = Bb + (size_t)tt * npad + i0;
+        const float* Cs = Cb + (size_t)tt * npad + i0;
+        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
+#pragma unroll
+        for (int i = 0; i < NP; i += 4) {
+          const float4 b4 = *reinterpret_cast<const float4*>(Bs + i);
+          Sr[i] = fmaf(decay, Sr[i], dx * b4.x);
+          Sr[i + 1] = fmaf(decay, Sr[i + 1], dx * b4.y);
+          Sr[i + 2] = fmaf(decay, Sr[i + 2], dx * b4.z);
+          Sr[i + 3] = fmaf(decay, Sr[i + 3], dx * b4.w);
+          if (MODE != 1) {
+            const float4 c4 = *reinterpret_cast<const float4*>(Cs + i);
+            y0 = fmaf(Sr[i], c4.x, y0);
+            y1 = fmaf(Sr[i + 1], c4.y, y1);
+            y2 = fmaf(Sr[i + 2], c4.z, y2);
+            y3 = fmaf(Sr[i + 3], c4.w, y3);
+          }
+        }
+        if (MODE != 1) {
+          float y = (y0 + y1) + (y2 + y3);
+          if (SPLIT >= 2) y += __shfl_xor_sync(0xffffffffu, y, 16);
+          if (SPLIT == 4) y += __shfl_xor_sync(0xffffffffu, y, 8);
+          if (i0 == 0 && j < dv) a.y[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = fmaf(Dh, xj, y);
+        }
+      }
+    } else if (j < dv) {
       for (int tt = 0; tt < nb; ++tt) {
         const float decay = s_a[tt];
         const float xj = xb[(size_t)tt * dv + j];
         const float dx = s_dt[tt] * xj;
         const float* Bs = Bb + (size_t)tt * npad;
         const float* Cs = Cb + (size_t)tt * npad;
-        float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
-        if (NREG > 0) {
-#pragma unroll
-          for (int i = 0; i < NP; i += 4) {
-            const float4 b4 = *reinterpret_cast<const float4*>(Bs + i);
-            Sr[i] = fmaf(decay, Sr[i], dx * b4.x);
-            Sr[i + 1] = fmaf(decay, Sr[i + 1], dx * b4.y);
-            Sr[i + 2] = fmaf(decay, Sr[i + 2], dx * b4.z);
-            Sr[i + 3] = fmaf(decay, Sr[i + 3], dx * b4.w);
-            if (MODE != 1) {
-              const float4 c4 = *reinterpret_cast<const float4*>(Cs + i);
-              y0 = fmaf(Sr[i], c4.x, y0);
-              y1 = fmaf(Sr[i + 1], c4.y, y1);
-              y2 = fmaf(Sr[i + 2], c4.z, y2);
-              y3 = fmaf(Sr[i + 3], c4.w, y3);
-            }
-          }
-        } else {
-          for (int i = 0; i < n; ++i) {
-            const float s = fmaf(decay, Ssm[(size_t)i * dv + j], dx * Bs[i]);
-            Ssm[(size_t)i * dv + j] = s;
-            if (MODE != 1) y0 = fmaf(s, Cs[i], y0);
-          }
+        float y0 = 0.f;
+        for (int i = 0; i < n; ++i) {
+          const float s = fmaf(decay, Ssm[(size_t)i * dv + j], dx * Bs[i]);
+          Ssm[(size_t)i * dv + j] = s;
+          if (MODE != 1) y0 = fmaf(s, Cs[i], y0);
         }
-        if (MODE != 1) a.y[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = fmaf(Dh, xj, (y0 + y1) + (y2 + y3));
+        if (MODE != 1) a.y[(size_t)(tb + tt) * a.heads * dv + head * dv + j] = fmaf(Dh, xj, y0);
       }
     }
   }
   __syncthreads();
   if (MODE == 3 && t1 != q1) return;               // only the sequence's last chunk leaves the state
   float* dst = MODE == 1 ? cs : gS;
-  if (NREG > 0) {
+  if (NR > 0) {
     if (j < dv) {
 #pragma unroll
       for (int i = 0; i < NP; ++i)
-        if (i < n) dst[(size_t)i * dv + j] = Sr[i];
+        if (i0 + i < n) dst[(size_t)(i0 + i) * dv + j] = Sr[i];
     }
   } else {
     for (int i = threadIdx.x; i < n * dv; i += blockDim.x) dst[i] = Ssm[i];
@@ -205,18 +225,19 @@ __global__ void gated_part_norm_kernel(const float* y, const T* z, long long z_l
   }
 }
 
-template <typename T, int NREG>
+template <typename T, int NR, int SPLIT>
 static int ssd_run(const SsdArgs& a, cudaStream_t stream) {
   const int n = a.n, dv = a.dv;
-  const int npad = NREG > 0 ? NREG : n;
-  const size_t smem = ((NREG > 0 ? 0 : (size_t)n * dv) + 2 * (size_t)kSsdBatch * npad + (size_t)kSsdBatch * dv) * sizeof(float);
+  const int npad = NR > 0 ? NR * SPLIT : n;
+  const size_t smem = ((NR > 0 ? 0 : (size_t)n * dv) + 2 * (size_t)kSsdBatch * npad + (size_t)kSsdBatch * dv) * sizeof(float);
   if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
-  int threads = (dv + 31) / 32 * 32;
+  const int cols_per_warp = 32 / SPLIT;
+  int threads = (dv + cols_per_warp - 1) / cols_per_warp * 32;
   if (threads < 32) threads = 32;
-  if (threads > (NREG == 0 ? 1024 : 512)) return PE_ERR_UNSUPPORTED_SIZE;
-  auto k0 = ssd_kernel<T, 0, NREG>;
-  auto k1 = ssd_kernel<T, 1, NREG>;
-  auto k3 = ssd_kernel<T, 3, NREG>;
+  if (threads > (NR == 0 ? 1024 : 512)) return PE_ERR_UNSUPPORTED_SIZE;
+  auto k0 = ssd_kernel<T, 0, NR, SPLIT>;
+  auto k1 = ssd_kernel<T, 1, NR, SPLIT>;
+  auto k3 = ssd_kernel<T, 3, NR, SPLIT>;
   if (smem > 48 * 1024) {
     cudaError_t e = cudaFuncSetAttribute(k0, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e == cudaSuccess) e = cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
@@ -234,6 +255,20 @@ static int ssd_run(const SsdArgs& a, cudaStream_t stream) {
     launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a);
   }
   return PE_OK;
+}
+
+// Threads a column and rows a thread for a state of n rows and dv columns: as many threads a column as the rows are worth
+// (four from 65 rows on, two from 33) and a block of at most 512 threads allows; 0 rows: the shared-memory form.
+static void ssd_shape(int n, int dv, int* rows, int* split) {
+  int s = n > 64 ? 4 : (n > 32 ? 2 : 1);
+  while (s > 1 && (dv + 32 / s - 1) / (32 / s) * 32 > 512) s /= 2;
+  const int per = (n + s - 1) / s;
+  int r = per <= 16 ? 16 : (per <= 32 ? 32 : (per <= 64 ? 64 : (per <= 128 ? 128 : 0)));
+  if (s == 1 && dv > 512) r = 0;
+  if (s == 2 && r == 16) r = 32;
+  if (s == 4 && r == 16) r = 32;
+  if (s > 1 && r == 128) { r = 0; s = 1; }
+  *rows = r; *split = r == 0 ? 1 : s;
 }
 
 }  // namespace pe
@@ -260,12 +295,15 @@ extern "C" int pe_ssd_recurrence(int dtype, const void* xbc, long long xbc_ld, c
     if (!scratch || max_chunks <= 0 || (long long)max_chunks * chunk < max_q || max_chunks > 65535) return PE_ERR_BAD_ARGUMENT;
     args.chunk = chunk; args.max_chunks = max_chunks; args.scratch = scratch;
   }
-  const int reg = (dv > 512) ? 0 : (n <= 16 ? 16 : (n <= 32 ? 32 : (n <= 64 ? 64 : (n <= 128 ? 128 : 0))));
+  int rows = 0, split = 1;
+  pe::ssd_shape(n, dv, &rows, &split);
   int rc;
-#define PE_SSD(T)                                                                                  \
-  (reg == 16 ? pe::ssd_run<T, 16>(args, stream) : reg == 32 ? pe::ssd_run<T, 32>(args, stream)      \
-   : reg == 64 ? pe::ssd_run<T, 64>(args, stream) : reg == 128 ? pe::ssd_run<T, 128>(args, stream)  \
-   : pe::ssd_run<T, 0>(args, stream))
+#define PE_SSD(T)                                                                                                   \
+  (split == 4 ? (rows == 32 ? pe::ssd_run<T, 32, 4>(args, stream) : pe::ssd_run<T, 64, 4>(args, stream))            \
+   : split == 2 ? (rows == 32 ? pe::ssd_run<T, 32, 2>(args, stream) : pe::ssd_run<T, 64, 2>(args, stream))          \
+   : rows == 16 ? pe::ssd_run<T, 16, 1>(args, stream) : rows == 32 ? pe::ssd_run<T, 32, 1>(args, stream)            \
+   : rows == 64 ? pe::ssd_run<T, 64, 1>(args, stream) : rows == 128 ? pe::ssd_run<T, 128, 1>(args, stream)          \
+   : pe::ssd_run<T, 0, 1>(args, stream))
   rc = dtype == PE_F32 ? PE_SSD(float) : PE_SSD(__nv_bfloat16);
 #undef PE_SSD
   if (rc != PE_OK) return rc;

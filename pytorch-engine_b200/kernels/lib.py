@@ -82,7 +82,7 @@ _SIGNATURES = {
     "pe_rmsnorm_residual_sum": [I, P, P, P, I, P, P, P, I, I, F, P],
     "pe_mlstm_recurrence": [I, P, P, P, P, L, P, P, P, F, F, F, P, P, P, P, P, P, I, I, I, I, I, I, I, I, P, P, P],
     "pe_short_conv_silu": [I, P, L, I, P, P, I, P, P, P, P, P, I, I, I, I, P, P],
-    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, P, P],
+    "pe_delta_rule_recurrence": [I, P, P, P, P, P, P, L, P, F, F, P, P, P, P, I, I, I, I, I, I, I, I, I, P, I, I, L, L, P, P],
     "pe_moe_route": [P, P, I, I, I, P, P, P, I, P],
     "pe_moe_group": [P, I, I, I, P, P, P, P],
     "pe_moe_rows_gemm": [I, I, P, L, P, P, I, I, P, L, P, L, I, I, I, F, F, P],
@@ -100,6 +100,7 @@ _SIGNATURES = {
     "pe_dyt_add": [I, P, P, P, P, F, P, P, F, P, I, I, P],
     "pe_rmsnorm_pair_mix": [I, P, P, P, P, F, F, F, P, I, I, P],
     "pe_concat_split": [I, P, P, P, P, I, I, P],
+    "pe_rmsnorm_pair_mix_dyt_add": [I, P, P, P, P, F, F, F, P, P, P, F, P, P, F, P, I, I, P],
     "pe_norm_token_shift": [I, P, P, F, P, P, P, P, P, P, I, I, I, P, P],
     "pe_depth_average": [P, L, P, I, P, P, L, P],
     "pe_polynorm": [I, P, P, F, P, I, I, P],

@@ -697,18 +697,18 @@ def delta_rule_recurrence(qkv: torch.Tensor, a: torch.Tensor, dt_bias: torch.Ten
                           kv_heads: int, d: int, dv: int, status: torch.Tensor, chunk: int = 0, max_chunks: int = 1,
                           scratch: Optional[torch.Tensor] = None, head_decay: bool = False, gate_silu: bool = False) -> None:
     """csrc/delta_rule.cu.  ``qkv [N, 2 * kv_heads * d + heads * dv]`` after the convolutions; ``a [N, heads * d]`` and
-    ``b [N, heads]`` float32; ``gate [N, heads * dv]`` in the run dtype (any row stride).  ``chunk`` > 0: prompts cut into
+    ``b [N, heads]`` float32 (any row strides); ``gate [N, heads * dv]`` in the run dtype (any row stride).  ``chunk`` > 0: prompts cut into
     chunks of that many tokens that run side by side (``scratch``: float32, ``delta_rule_scratch_floats`` of them).
     ``head_decay``: one decay per head (``a [N, heads]``, ``dt_bias [heads]``); ``gate_silu``: silu instead of sigmoid."""
     _need(a.shape[1] == (heads if head_decay else heads * d) and dt_bias.numel() == a.shape[1], "delta_rule: the decay's layout")
     _need(qkv.is_contiguous() and qkv.shape[1] == 2 * kv_heads * d + heads * dv, "delta_rule: q|k|v layout")
-    _need(a.dtype == torch.float32 and a.is_contiguous() and b.dtype == torch.float32 and b.is_contiguous(), "delta_rule: a, b f32")
+    _need(a.dtype == torch.float32 and a.stride(1) == 1 and b.dtype == torch.float32 and b.stride(1) == 1, "delta_rule: a, b f32")
     _need(gate.stride(1) == 1 and gate.dtype == qkv.dtype and out.is_contiguous() and S.is_contiguous(), "delta_rule: layouts")
     check(library().pe_delta_rule_recurrence(dtype_tag(qkv.dtype), _ptr(qkv), _ptr(a), _ptr(dt_bias), _ptr(A_log), _ptr(b),
                                              _ptr(gate), gate.stride(0), _ptr(norm_w), float(eps), float(q_scale), _ptr(out),
                                              _ptr(S), _ptr(seq_slot), _ptr(seq_qstart), n_seqs, int(max_q), heads, kv_heads, d, dv,
                                              S.shape[0], int(chunk), int(max_chunks), _ptr(scratch), 1 if head_decay else 0,
-                                             1 if gate_silu else 0, _ptr(status), _stream()),
+                                             1 if gate_silu else 0, a.stride(0), b.stride(0), _ptr(status), _stream()),
           "delta_rule_recurrence")
     _count(3 if chunk > 0 else 1)
 
@@ -1032,4 +1032,24 @@ def concat_split(a: torch.Tensor, b: torch.Tensor, hi: torch.Tensor, lo: Optiona
     _need(hi.is_contiguous() and tuple(hi.shape) == (n, 2 * dim) and (lo is None or (lo.is_contiguous() and lo.shape == hi.shape
                                                                                    and lo.dtype == hi.dtype)), "concat_split: outputs")
     check(library().pe_concat_split(dtype_tag(hi.dtype), _ptr(a), _ptr(b), _ptr(hi), _ptr(lo), n, dim, _stream()), "concat_split")
+    _count(1)
+
+
+def rmsnorm_pair_mix_dyt_add(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, eps: float, sa: float, sb: float,
+                             stream: torch.Tensor, post, next_norm=None, out: Optional[torch.Tensor] = None) -> None:
+    """``m = sa * unit(a) * wa + sb * unit(b) * wb``; ``stream += tanh(alpha * m) * w + b`` with ``post = (w, b, alpha)``; with
+    ``next_norm = (w2, b2, alpha2)`` and ``out``: ``out = tanh(alpha2 * stream) * w2 + b2`` of the new rows, all in one pass
+    (csrc/dyt.cu)."""
+    n, dim = a.shape
+    _need(a.is_contiguous() and b.is_contiguous() and a.shape == b.shape and a.dtype == b.dtype, "pair_mix_dyt_add: inputs")
+    _need(stream.dtype == torch.float32 and stream.is_contiguous() and tuple(stream.shape) == (n, dim), "pair_mix_dyt_add: stream")
+    w1, b1, a1 = post
+    w2 = b2 = None
+    a2 = 0.0
+    if out is not None:
+        w2, b2, a2 = next_norm
+        _need(out.dtype == a.dtype and out.is_contiguous() and tuple(out.shape) == (n, dim), "pair_mix_dyt_add: out")
+    check(library().pe_rmsnorm_pair_mix_dyt_add(dtype_tag(a.dtype), _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), float(eps), float(sa),
+                                                float(sb), _ptr(stream), _ptr(w1), _ptr(b1), float(a1), _ptr(w2), _ptr(b2), float(a2),
+                                                _ptr(out), n, dim, _stream()), "rmsnorm_pair_mix_dyt_add")
     _count(1)

@@ -252,6 +252,15 @@ class SandwichBlock:
             outs.append(out)
         mixed = outs[0]
         if len(outs) == 2:
+            if getattr(self.post_mixer_norm, "tanh_norm", False) and hasattr(self.combine, "add_after_tanh_norm") and (
+                    self.ffn is None or getattr(self.ffn_norm, "tanh_norm", False)):
+                # the two outputs' mix, the norm on it, the add and the feed-forward's norm in one kernel
+                self.combine.add_after_tanh_norm(outs[0], outs[1], stream, self.post_mixer_norm, self.ffn_norm,
+                                                 None if self.ffn is None else normed)
+                if self.ffn is not None:
+                    self.post_ffn_norm.add_after(stream, self.ffn.forward(normed, ctx), None)
+                ctx.stream_copy = None
+                return None
             mixed = self.combine.forward(outs[0], outs[1], ctx.buffer("block.mixed", tuple(outs[0].shape), outs[0].dtype))
         if self.ffn is None:
             self.post_mixer_norm.add_after(stream, mixed, None)

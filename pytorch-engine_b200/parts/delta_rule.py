@@ -173,10 +173,7 @@ class GatedDeltaMixer:
         rt = self.runtime
         n, nh = x.shape[0], self.n_heads
         ba = self._f32_linear(x, self.b_proj, ctx.buffer("delta.beta_decay", (n, 2 * nh), torch.float32))
-        beta = ctx.buffer("delta.beta", (n, nh), torch.float32)
-        decay = ctx.buffer("delta.decay", (n, nh), torch.float32)
-        beta.copy_(ba[:, :nh])
-        decay.copy_(ba[:, nh:])
+        beta, decay = ba[:, :nh], ba[:, nh:]       # the kernel takes rows of any stride
         gate = wide[:, self.channels:]
         out = ctx.buffer("delta.out", (n, nh * self.v_dim), rt.dtype)
         chunk, max_chunks, scratch = 0, 1, None

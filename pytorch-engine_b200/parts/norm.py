@@ -54,6 +54,7 @@ class DynamicTanh:
     (csrc/dyt.cu).  params: ``dim``.  weights: ``weight [dim]``, ``bias [dim]``, ``alpha []``."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
+    tanh_norm = True   # other parts may take (weight, bias, alpha) into a kernel of their own
 
     @classmethod
     def weight_decls(cls, params) -> Dict[str, WeightDecl]:

@@ -141,3 +141,11 @@ class NormedMean:
     def forward(self, a: torch.Tensor, b: torch.Tensor, out: torch.Tensor) -> torch.Tensor:
         ops.rmsnorm_pair_mix(a, b, self.weight_a, self.weight_b, self.eps, self.scale, self.scale, out)
         return out
+
+    def add_after_tanh_norm(self, a: torch.Tensor, b: torch.Tensor, stream: torch.Tensor, post, then=None,
+                            out: Optional[torch.Tensor] = None) -> None:
+        """The mix, the Dynamic Tanh norm ``post`` on it, the add into ``stream`` and (``then`` with ``out``) the norm in front
+        of the next sublayer, in one kernel; ``post`` and ``then`` are ``DynamicTanh`` parts."""
+        nxt = None if then is None or out is None else (then.weight, then.bias, then.alpha)
+        ops.rmsnorm_pair_mix_dyt_add(a, b, self.weight_a, self.weight_b, self.eps, self.scale, self.scale, stream,
+                                     (post.weight, post.bias, post.alpha), nxt, out if nxt else None)

@@ -70,30 +70,45 @@ def tanh_norm(x: torch.Tensor, w: Dict[str, torch.Tensor], name: str) -> torch.T
 
 
 # ---- feed-forward ---------------------------------------------------------------------------------------------
-def router_choice(scores: torch.Tensor, r: dict):
-    """``scores [T, E]`` -> (chosen [T, top] indices, their scores)."""
+def router_choice(scores: torch.Tensor, r: dict, margins: Optional[list] = None):
+    """``scores [T, E]`` -> (chosen [T, top] indices, their scores).  ``margins`` (a list) gets one tensor ``[T]``: by how much
+    the choice was decided, in units of the router's logits: the smaller of the gap between the last kept and the first dropped
+    group and the gap between the last chosen expert and the best one left out, each divided by how far the scores involved
+    move per unit of their logits, ``s (1 - s)`` (an error of that size in the logits would have chosen otherwise)."""
     T, E = scores.shape
     top = int(r["top"])
     allowed = torch.ones_like(scores, dtype=torch.bool)
+    margin = torch.full((T,), float("inf"), dtype=scores.dtype)
     groups = r.get("groups")
     if groups:
         count, keep = int(groups["count"]), int(groups["keep"])
         per = E // count
         g = scores.view(T, count, per)
-        gscore = g.topk(min(2, per), dim=-1).values.sum(-1)
-        best = gscore.topk(keep, dim=-1).indices
+        gtop = g.topk(min(2, per), dim=-1).values
+        gscore = gtop.sum(-1)
+        ranked = gscore.topk(count, dim=-1)
+        if keep < count:
+            moves = (gtop * (1 - gtop)).sum(-1).gather(1, ranked.indices[:, keep - 1:keep + 1]).sum(-1)
+            margin = (ranked.values[:, keep - 1] - ranked.values[:, keep]) / (moves + 1e-12)
         gmask = torch.zeros(T, count, dtype=torch.bool)
-        gmask.scatter_(1, best, True)
+        gmask.scatter_(1, ranked.indices[:, :keep], True)
         allowed = gmask[:, :, None].expand(T, count, per).reshape(T, E)
     masked = torch.where(allowed, scores, torch.full_like(scores, -1.0))
-    chosen = masked.topk(top, dim=-1).indices
+    ranked = masked.topk(min(top + 1, E), dim=-1)
+    if top < E:
+        last, left_out = ranked.values[:, top - 1], ranked.values[:, top]
+        gap = (last - left_out) / (last * (1 - last) + left_out * (1 - left_out) + 1e-12)
+        margin = torch.minimum(margin, torch.where(left_out >= 0, gap, margin))
+    if margins is not None:
+        margins.append(margin)
+    chosen = ranked.indices[:, :top]
     return chosen, scores.gather(1, chosen)
 
 
-def moe_ff(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor], p: str) -> torch.Tensor:
+def moe_ff(h: torch.Tensor, mlp: dict, w: Dict[str, torch.Tensor], p: str, margins: Optional[list] = None) -> torch.Tensor:
     r = mlp["router"]
     scores = torch.sigmoid(h @ w[f"{p}.router"].T)
-    chosen, weight = router_choice(scores, r)
+    chosen, weight = router_choice(scores, r, margins)
     out = torch.zeros_like(h)
     for t in range(h.shape[0]):
         for e, s in zip(chosen[t].tolist(), weight[t]):
@@ -265,7 +280,7 @@ def run_order(cfg: dict) -> List[tuple]:
     return order + [(i, False) for i in range(b, n)]
 
 
-def layer(x: torch.Tensor, spec: dict, w: Dict[str, torch.Tensor], p: str, eps: float) -> torch.Tensor:
+def layer(x: torch.Tensor, spec: dict, w: Dict[str, torch.Tensor], p: str, eps: float, margins: Optional[list] = None) -> torch.Tensor:
     h = st(tanh_norm(x, w, f"{p}.norm1"))
     kind = spec["type"]
     if kind == "attention":
@@ -279,12 +294,14 @@ def layer(x: torch.Tensor, spec: dict, w: Dict[str, torch.Tensor], p: str, eps: 
     x = x + tanh_norm(y, w, f"{p}.norm1b")
     if spec.get("mlp") is not None:
         h = st(tanh_norm(x, w, f"{p}.norm2"))
-        x = x + tanh_norm(moe_ff(h, spec["mlp"], w, f"{p}.mlp"), w, f"{p}.norm2b")
+        x = x + tanh_norm(moe_ff(h, spec["mlp"], w, f"{p}.mlp", margins), w, f"{p}.norm2b")
     return x
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, streams: Optional[list] = None):
-    """Logits ``[T, vocab]`` of one sequence; ``streams`` (a list) collects the stream after every layer that ran."""
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torch.float64, streams: Optional[list] = None,
+            margins: Optional[list] = None):
+    """Logits ``[T, vocab]`` of one sequence; ``streams`` (a list) collects the stream after every layer that ran, ``margins``
+    (a list) one tensor ``[T]`` per routed feed-forward that ran: by how much its choice of experts was decided."""
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = float(cfg["norm"]["eps"])
     x = w["embed"][tokens] * float(cfg.get("embedding", {}).get("scale", 1.0))
@@ -292,7 +309,7 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens: List[int], dtype=torc
     for i, first in run_order(cfg):
         if first:
             x = torch.cat([x, x0], dim=-1) @ w["loop.in"].T
-        x = layer(x, cfg["layers"][i], w, f"l{i}", eps)
+        x = layer(x, cfg["layers"][i], w, f"l{i}", eps, margins)
         if streams is not None:
             streams.append(x.clone())
     return st(tanh_norm(x, w, "final.norm")) @ w["embed"].T

@@ -115,3 +115,28 @@ def test_cli_greedy_lunadra(pe, tmp_path, capsys):
         for j, tok in enumerate(r["token_ids"]):
             row = ref[len(p) - 1 + j]
             assert float(row.max() - row[tok]) <= 1e-4 * float(ref.abs().max())
+
+
+def test_cli_greedy_zonevik(pe, tmp_path, capsys):
+    """The fifth architecture through the same command line: a folder written from the preset (a looped range of layers,
+    window attention with kept first positions beside a state-space mixer, the gated delta rule, gated attention, experts
+    chosen among groups), greedy tokens in float32 against the plain implementation's best token at every step."""
+    import plain_zonevik
+    from safetensors.torch import load_file
+
+    folder = str(tmp_path / "z")
+    pe.write_random_model(folder, pe.preset("zonevik_tiny"), 7)
+    with open(folder + "/config.json") as fh:
+        cfg = json.load(fh)
+    w = {k: v.float() for k, v in load_file(folder + "/model.safetensors").items()}
+    prompts = _prompts(cfg["vocab"], (3, 11, 150), 3)
+    argv = ["--model", folder, "--dtype", "fp32", "--ctx", "256", "--max-tokens", "6", "--temperature", "0", "--json"]
+    for p in prompts:
+        argv += ["--prompt-ids", ",".join(map(str, p))]
+    out = _run_cli(capsys, argv)
+    for r, p in zip(out, prompts):
+        assert r["completion_tokens"] == 6
+        ref = plain_zonevik.forward(cfg, w, p + r["token_ids"])
+        for j, tok in enumerate(r["token_ids"]):
+            row = ref[len(p) - 1 + j]
+            assert float(row.max() - row[tok]) <= 1e-4 * float(ref.abs().max())

@@ -12,6 +12,12 @@ from conftest import rel_err
 pytestmark = pytest.mark.gpu
 DEV = "cuda:0"
 TOL = {"float32": 3e-5, "bfloat16": 2e-2}
+# a gap between two experts' (or two groups') scores, in units of the router's logits, below which a bfloat16 rounding may
+# choose otherwise
+CLOSE_CALL = 0.01
+# positions behind one whose nearly tied choice fell the other way that are left out with it (the convolutions' taps, the
+# recurrent state and the window carry the other expert's output on)
+AFTER_A_CLOSE_CALL = 3
 
 
 def _att(heads, kv, dim, vdim, scale, dims=0, base=10000.0, scaling=None):
@@ -107,8 +113,16 @@ class Models:
     def ref(self, key, toks):
         ident = (key, tuple(toks))
         if ident not in self.refs:
-            self.refs[ident] = plain.forward(self.configs[key], self.w(key), toks).float()
+            margins = []
+            self.refs[ident] = plain.forward(self.configs[key], self.w(key), toks, margins=margins).float()
+            self.refs[ident + ("decided",)] = (torch.stack(margins).min(0).values if margins
+                                               else torch.full((len(toks),), float("inf"), dtype=torch.float64))
         return self.refs[ident]
+
+    def decided(self, key, toks):
+        """Per position: the smallest gap by which any router of the model chose its experts there."""
+        self.ref(key, toks)
+        return self.refs[(key, tuple(toks), "decided")]
 
     def noise(self, key, toks):
         """How far rounding to bfloat16 alone moves each position's logits (root mean square over the vocabulary)."""
@@ -122,9 +136,10 @@ class Models:
     def check(self, key, dtype, toks, got, positions, what):
         """float32: every logit within 3e-5 of the largest.  bfloat16: the error is held against what rounding alone does
         in the plain implementation: on average no more than twice that, and at no more than one position in fifty (or
-        one) above three times the larger of that position's own figure and the average.  The average leaves the worst
-        position out: where two experts' scores nearly tie, a rounding picks the other one, which moves that one position by
-        ten times what rounding does elsewhere (it stays counted among the positions that may lie above)."""
+        one) above three times the larger of that position's own figure and the average.  Positions where a router's choice
+        hung on a gap of less than CLOSE_CALL (in the router's logits) between two scores are left out: there a rounding may
+        pick another expert, which moves that position by ten times what rounding does elsewhere; where it did, the
+        AFTER_A_CLOSE_CALL positions behind it are left out too.  The average also leaves the worst position out."""
         positions = list(positions)
         ref = self.ref(key, toks)[positions]
         got = got.float().cpu()
@@ -133,6 +148,19 @@ class Models:
             err = float((got.double() - ref.double()).abs().max() / ref.double().abs().max())
             assert err < TOL[dtype], f"{what}: error {err:.3e} (limit {TOL[dtype]:.0e})"
             return
+        noise = self.noise(key, toks)
+        floor = float(noise.mean())
+        tied = self.decided(key, toks) < CLOSE_CALL
+        all_err = (got.double() - ref.double()).pow(2).mean(dim=1).sqrt()
+        left_out = set()
+        for p, e in zip(positions, all_err.tolist()):
+            if bool(tied[p]):
+                left_out.add(p)
+                if e > 3.0 * max(float(noise[p]), floor):          # it fell the other way: the next few positions feel it
+                    left_out.update(range(p + 1, p + 1 + AFTER_A_CLOSE_CALL))
+        keep = [i for i, p in enumerate(positions) if p not in left_out]
+        assert len(keep) >= max(1, len(positions) // 4), f"{what}: too many positions with nearly tied experts"
+        positions, got, ref = [positions[i] for i in keep], got[keep], ref[keep]
         noise = self.noise(key, toks)
         err = (got.double() - ref.double()).pow(2).mean(dim=1).sqrt()
         floor = float(noise.mean())
@@ -160,11 +188,12 @@ def _batch(q_lens, slots):
 
 
 # ---- mechanisms at kernel level -----------------------------------------------------------------------------------
+@pytest.mark.parametrize("dim", [50, 72])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_tanh_norm_alone_with_its_add_and_the_next_norm(pe, dtype):
+def test_tanh_norm_alone_with_its_add_and_the_next_norm(pe, dtype, dim):
     ops = pe.kernels.ops
     g = torch.Generator().manual_seed(1)
-    n, dim = 37, 50
+    n = 37
     x = torch.randn(n, dim, generator=g) * 3
     d = (torch.randn(n, dim, generator=g) * 2).to(dtype)
     w = {f"n{i}{s}": torch.randn(dim, generator=g) for i in (1, 2) for s in ("", ".b")}
@@ -180,6 +209,24 @@ def test_tanh_norm_alone_with_its_add_and_the_next_norm(pe, dtype):
     want = x.double() + plain.tanh_norm(d.double(), w, "n1")
     assert (stream.cpu() - want).abs().max() < 1e-5
     assert (nxt.float().cpu() - plain.tanh_norm(want, w, "n2")).abs().max() < tol
+    # two outputs side by side: each over its own root mean square, weighted, half their sum; alone, and with the norm on
+    # it, the add and the next norm in the same kernel
+    e = (torch.randn(n, dim, generator=g) * 0.3).to(dtype)
+    wa, wb = torch.randn(dim, generator=g), torch.randn(dim, generator=g)
+    mix = 0.5 * (plain.unit(d.double(), 1e-5) * wa + plain.unit(e.double(), 1e-5) * wb)
+    out = torch.empty(n, dim, dtype=dtype, device=DEV)
+    ops.rmsnorm_pair_mix(d.to(DEV), e.to(DEV), wa.to(DEV), wb.to(DEV), 1e-5, 0.5, 0.5, out)
+    assert (out.float().cpu() - mix).abs().max() < tol
+    for with_next in (False, True):
+        stream = x.clone().to(DEV)
+        nxt.fill_(float("nan"))
+        ops.rmsnorm_pair_mix_dyt_add(d.to(DEV), e.to(DEV), wa.to(DEV), wb.to(DEV), 1e-5, 0.5, 0.5, stream,
+                                     (w["n1"].to(DEV), w["n1.b"].to(DEV), 0.7),
+                                     (w["n2"].to(DEV), w["n2.b"].to(DEV), 1.9) if with_next else None, nxt if with_next else None)
+        want = x.double() + plain.tanh_norm(mix, w, "n1")
+        assert (stream.cpu() - want).abs().max() < 1e-5
+        if with_next:
+            assert (nxt.float().cpu() - plain.tanh_norm(want, w, "n2")).abs().max() < tol
 
 
 def test_router_groups_two_best_scores_kept_groups_and_plain_scores_as_weights(pe):
@@ -283,7 +330,7 @@ def test_keys_at_the_edges_of_the_window_and_of_the_kept_positions(pe, decode, w
             assert (out[-1:].float().cpu() - want).abs().max() < (1e-3 if dt == torch.float32 else 3e-2), (decode, window, keep, n, target, seen)
 
 
-@pytest.mark.parametrize("n_state,dv", [(8, 8), (24, 20), (64, 48), (128, 64), (136, 12), (40, 100)])
+@pytest.mark.parametrize("n_state,dv", [(8, 8), (24, 20), (64, 48), (128, 64), (136, 12), (40, 100), (300, 8), (100, 260), (16, 600)])
 def test_state_space_recurrence_whole_chunked_in_steps_and_on_kept_state(pe, n_state, dv):
     """Whole sequences (short: one go; long: chunks side by side) against the same sequences cut into steps of 1, 3 and many
     tokens, two sequences of unequal length on slots whose neighbours hold other state, against the plain recurrence."""
