@@ -31,6 +31,38 @@ struct SsdArgs {
 
 constexpr int kSsdBatch = 32;
 
+// A staged B or C row with SPLIT threads a column: part p's rows [p * NP, (p + 1) * NP) start 4 floats further on for every
+// part before them, so the four parts' 16-byte reads of one step (one address a quarter-warp) fall into different banks.
+__host__ __device__ inline int ssd_row_floats(int np, int split) { return split == 1 ? np : split * (np + 4); }
+
+// dst[r][col(c)] = float(src[r][c]) with col(c) = c + 4 * (c / np) (np == 0: col(c) = c)
+template <typename T>
+__device__ __forceinline__ void ssd_stage_rows(float* dst, int dst_ld, int np, const T* src, long long src_ld, int n_rows, int width,
+                                               bool vec) {
+  if (vec) {
+    constexpr int N = StageVec<T>::N;
+    const int per_row = width / N;
+    for (int e = threadIdx.x; e < n_rows * per_row; e += blockDim.x) {
+      const int r = e / per_row, c = (e - r * per_row) * N;
+      const uint4 raw = *reinterpret_cast<const uint4*>(src + (size_t)r * src_ld + c);
+      float* o = dst + (size_t)r * dst_ld + (np > 0 ? c + 4 * (c / np) : c);
+      if (sizeof(T) == 4) {
+        *reinterpret_cast<float4*>(o) = *reinterpret_cast<const float4*>(&raw);
+      } else {
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]), c2 = __bfloat1622float2(h[2]), d2 = __bfloat1622float2(h[3]);
+        *reinterpret_cast<float4*>(o) = make_float4(a.x, a.y, b.x, b.y);
+        *reinterpret_cast<float4*>(o + 4) = make_float4(c2.x, c2.y, d2.x, d2.y);
+      }
+    }
+  } else {
+    for (int e = threadIdx.x; e < n_rows * width; e += blockDim.x) {
+      const int r = e / width, c = e - r * width;
+      dst[(size_t)r * dst_ld + (np > 0 ? c + 4 * (c / np) : c)] = to_f32<T>(src[(size_t)r * src_ld + c]);
+    }
+  }
+}
+
 // MODE 0: the whole step from the slot's state; MODE 1: chunk blockIdx.z from an empty state, no outputs; MODE 3: chunk
 // blockIdx.z from its true start, outputs, and the sequence's last chunk writes the state back.
 // NR > 0: a thread keeps NR rows of its column in registers and SPLIT threads share a column (lanes l, l ^ 16 for two,
@@ -44,11 +76,13 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
   const int n = a.n, dv = a.dv, head = blockIdx.x, b = blockIdx.y, c = blockIdx.z;
   const int g = head / (a.heads / a.groups);
   constexpr int NP = NR > 0 ? NR : 1;
-  const int npad = NR > 0 ? NR * SPLIT : n;
+  const int npad = NR > 0 ? NR * SPLIT : n;                    // rows with the padding up to what the threads hold
+  const int ldb = NR > 0 ? ssd_row_floats(NR, SPLIT) : n;      // floats of a staged B or C row
+  const int part_np = (NR > 0 && SPLIT > 1) ? NR : 0;          // rows a part (0: the row is not cut into parts)
   float* Ssm = sm;                                             // [n][dv] (NR == 0 only)
-  float* Bb = Ssm + (NR > 0 ? 0 : (size_t)n * dv);             // [batch][npad]
-  float* Cb = Bb + (size_t)kSsdBatch * npad;                   // [batch][npad]
-  float* xb = Cb + (size_t)kSsdBatch * npad;                   // [batch][dv]
+  float* Bb = Ssm + (NR > 0 ? 0 : (size_t)n * dv);             // [batch][ldb]
+  float* Cb = Bb + (size_t)kSsdBatch * ldb;                    // [batch][ldb]
+  float* xb = Cb + (size_t)kSsdBatch * ldb;                    // [batch][dv]
   pdl_wait_block();
   pdl_launch_dependents();
   const int slot = a.seq_slot[b];
@@ -72,7 +106,9 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
   const int lane = threadIdx.x & 31;
   // the thread's column and the first of its rows
   const int j = SPLIT == 1 ? (int)threadIdx.x : (int)(threadIdx.x >> 5) * (32 / SPLIT) + (lane & (32 / SPLIT - 1));
-  const int i0 = SPLIT == 1 ? 0 : (lane / (32 / SPLIT)) * NP;
+  const int part = SPLIT == 1 ? 0 : lane / (32 / SPLIT);
+  const int i0 = part * NP;
+  const int s0 = SPLIT == 1 ? 0 : part * (NP + 4);             // where the part's rows start in a staged row
   float Sr[NP];
   if (NR > 0) {
 #pragma unroll
@@ -83,22 +119,23 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
   if (npad > n)
     for (int e = threadIdx.x; e < kSsdBatch * (npad - n); e += blockDim.x) {
       const int tt = e / (npad - n), i = n + e % (npad - n);
-      Bb[(size_t)tt * npad + i] = 0.f;
-      Cb[(size_t)tt * npad + i] = 0.f;
+      const int at = part_np > 0 ? i + 4 * (i / part_np) : i;
+      Bb[(size_t)tt * ldb + at] = 0.f;
+      Cb[(size_t)tt * ldb + at] = 0.f;
     }
   const T* x = (const T*)a.xbc;
   const int b_col = a.heads * dv + g * n, c_col = a.heads * dv + a.groups * n + g * n, x_col = head * dv;
   const float rate = expf(a.A_log[head]), bias = a.dt_bias[head], Dh = a.D[head];
   const bool sm_ok = NR > 0 || (n * dv) % 4 == 0;   // the staged rows start on 16-byte boundaries
-  const bool vec_b = sm_ok && npad % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + b_col, a.xbc_ld, n);
-  const bool vec_c = sm_ok && npad % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + c_col, a.xbc_ld, n);
+  const bool vec_b = sm_ok && ldb % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + b_col, a.xbc_ld, n);
+  const bool vec_c = sm_ok && ldb % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + c_col, a.xbc_ld, n);
   const bool vec_x = sm_ok && dv % 4 == 0 && stage_vec_ok<T>(x + (size_t)t0 * a.xbc_ld + x_col, a.xbc_ld, dv);
   float log_sum = 0.f;
   for (int tb = t0; tb < t1; tb += kSsdBatch) {
     const int nb = min(kSsdBatch, t1 - tb);
     __syncthreads();                               // the batch before this one has been read
-    stage_rows_f32<T>(Bb, npad, x + (size_t)tb * a.xbc_ld + b_col, a.xbc_ld, nb, n, 1.f, vec_b);
-    if (MODE != 1) stage_rows_f32<T>(Cb, npad, x + (size_t)tb * a.xbc_ld + c_col, a.xbc_ld, nb, n, 1.f, vec_c);
+    ssd_stage_rows<T>(Bb, ldb, part_np, x + (size_t)tb * a.xbc_ld + b_col, a.xbc_ld, nb, n, vec_b);
+    if (MODE != 1) ssd_stage_rows<T>(Cb, ldb, part_np, x + (size_t)tb * a.xbc_ld + c_col, a.xbc_ld, nb, n, vec_c);
     stage_rows_f32<T>(xb, dv, x + (size_t)tb * a.xbc_ld + x_col, a.xbc_ld, nb, dv, 1.f, vec_x);
     if (threadIdx.x < nb) {
       const float z = to_f32<T>(((const T*)a.dt)[(size_t)(tb + threadIdx.x) * a.dt_ld + head]) + bias;
@@ -116,8 +153,8 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
         const float decay = s_a[tt];
         const float xj = j < dv ? xb[(size_t)tt * dv + j] : 0.f;
         const float dx = s_dt[tt] * xj;
-        const float* Bs = Bb + (size_t)tt * npad + i0;
-        const float* Cs = Cb + (size_t)tt * npad + i0;
+        const float* Bs = Bb + (size_t)tt * ldb + s0;
+        const float* Cs = Cb + (size_t)tt * ldb + s0;
         float y0 = 0.f, y1 = 0.f, y2 = 0.f, y3 = 0.f;
 #pragma unroll
         for (int i = 0; i < NP; i += 4) {
@@ -146,8 +183,8 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
         const float decay = s_a[tt];
         const float xj = xb[(size_t)tt * dv + j];
         const float dx = s_dt[tt] * xj;
-        const float* Bs = Bb + (size_t)tt * npad;
-        const float* Cs = Cb + (size_t)tt * npad;
+        const float* Bs = Bb + (size_t)tt * ldb;
+        const float* Cs = Cb + (size_t)tt * ldb;
         float y0 = 0.f;
         for (int i = 0; i < n; ++i) {
           const float s = fmaf(decay, Ssm[(size_t)i * dv + j], dx * Bs[i]);
@@ -184,18 +221,29 @@ __global__ void ssd_chain_kernel(SsdArgs a) {
   const int q_len = a.seq_qstart[b + 1] - a.seq_qstart[b];
   const int n_chunks = (q_len + a.chunk - 1) / a.chunk;
   const size_t unit = (size_t)a.n * a.dv;
-  const float* logs = a.scratch + (size_t)a.n_seqs * a.max_chunks * a.heads * unit;
+  const size_t per = (size_t)a.heads * unit;          // floats from one chunk's state to the next one's
+  const float* logs = a.scratch + (size_t)a.n_seqs * a.max_chunks * a.heads * unit + (size_t)b * a.max_chunks * a.heads + head;
   const float* gS = a.S + ((size_t)slot * a.heads + head) * unit;
-  for (size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x; e < unit; e += (size_t)gridDim.z * blockDim.x) {
-    float val = gS[e];
-    for (int c = 0; c < n_chunks; ++c) {
-      const size_t cidx = ((size_t)b * a.max_chunks + c) * a.heads + head;
-      float* u = a.scratch + cidx * unit + e;
-      const bool has = c + 1 < n_chunks;
-      const float loc = has ? *u : 0.f;
-      *u = val;
-      if (!has) break;
-      val = fmaf(expf(logs[cidx]), val, loc);
+  // a thread follows one element through the chunks, eight chunks' loads in flight at a time (a chunk's slot is read
+  // before it is overwritten with that chunk's true start)
+  constexpr int G = 8;
+  const size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
+  if (e >= unit) return;
+  float* u = a.scratch + ((size_t)b * a.max_chunks * a.heads + head) * unit + e;
+  float val = gS[e];
+  for (int c0 = 0; c0 < n_chunks; c0 += G) {
+    float loc[G], lg[G];
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      const bool has = c0 + i + 1 < n_chunks;
+      loc[i] = has ? u[(size_t)(c0 + i) * per] : 0.f;
+      lg[i] = has ? logs[(size_t)(c0 + i) * a.heads] : 0.f;
+    }
+#pragma unroll
+    for (int i = 0; i < G; ++i) {
+      if (c0 + i >= n_chunks) break;
+      u[(size_t)(c0 + i) * per] = val;
+      if (c0 + i + 1 < n_chunks) val = fmaf(expf(lg[i]), val, loc[i]);
     }
   }
 }
@@ -228,8 +276,8 @@ __global__ void gated_part_norm_kernel(const float* y, const T* z, long long z_l
 template <typename T, int NR, int SPLIT>
 static int ssd_run(const SsdArgs& a, cudaStream_t stream) {
   const int n = a.n, dv = a.dv;
-  const int npad = NR > 0 ? NR * SPLIT : n;
-  const size_t smem = ((NR > 0 ? 0 : (size_t)n * dv) + 2 * (size_t)kSsdBatch * npad + (size_t)kSsdBatch * dv) * sizeof(float);
+  const int ldb = NR > 0 ? ssd_row_floats(NR, SPLIT) : n;
+  const size_t smem = ((NR > 0 ? 0 : (size_t)n * dv) + 2 * (size_t)kSsdBatch * ldb + (size_t)kSsdBatch * dv) * sizeof(float);
   if (smem > 200 * 1024) return PE_ERR_UNSUPPORTED_SIZE;
   const int cols_per_warp = 32 / SPLIT;
   int threads = (dv + cols_per_warp - 1) / cols_per_warp * 32;
@@ -247,9 +295,9 @@ static int ssd_run(const SsdArgs& a, cudaStream_t stream) {
   if (a.chunk > 0) {
     launch(k1, dim3(a.heads, a.n_seqs, a.max_chunks), dim3(threads), smem, stream, a);
     const size_t unit = (size_t)n * dv;
-    int zb = (int)((unit + 255) / 256);
-    if (zb > 8) zb = 8;
-    launch(ssd_chain_kernel, dim3(a.heads, a.n_seqs, zb), dim3(256), 0, stream, a);
+    const size_t zb = (unit + 255) / 256;
+    if (zb > 65535) return PE_ERR_UNSUPPORTED_SIZE;
+    launch(ssd_chain_kernel, dim3(a.heads, a.n_seqs, (unsigned)zb), dim3(256), 0, stream, a);
     launch(k3, dim3(a.heads, a.n_seqs, a.max_chunks), dim3(threads), smem, stream, a);
   } else {
     launch(k0, dim3(a.heads, a.n_seqs, 1), dim3(threads), smem, stream, a);
