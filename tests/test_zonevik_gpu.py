@@ -75,8 +75,15 @@ CONFIGS = {
               {"type": "parallel", "mixer": {"left": _left(2, 1, 8, 12, 0.5, 64, 0), "right": _right(2, 12, 136, 2, 2, 2)}, "mlp": None},
               {"type": "parallel", "mixer": {"left": _left(1, 1, 40, 8, 0.2, 20, 33), "right": _right(1, 100, 8, 1, 4, 5)},
                "mlp": _moe(3, 2, 20, (3, 2))}]},
+    # D: nothing is a multiple of 4: no kernel may take its 16-byte paths; five taps; the last layer alone runs twice
+    "D": {"architecture": "Zonevik", "vocab": 77, "width": 54, "norm": {"eps": 3e-6}, "embedding": {"scale": 2.5},
+          "loop": {"start": 2, "stop": 3, "times": 2},
+          "layers": [
+              {"type": "attention", "mixer": _att(3, 1, 10, 6, 0.3, 6, 100.0, (3.0, 16, 4.0, 1.0)), "mlp": _moe(3, 2, 10)},
+              {"type": "parallel", "mixer": {"left": _left(2, 2, 6, 10, 0.4, 5, 2), "right": _right(3, 6, 5, 3, 5, 9)}, "mlp": None},
+              {"type": "delta", "mixer": {"heads": 2, "kv_heads": 2, "dim": 6, "vdim": 10, "conv": 5}, "mlp": _moe(6, 3, 14, (2, 1))}]},
 }
-SEEDS = {"A": 31, "B": 32, "C": 33}
+SEEDS = {"A": 31, "B": 32, "C": 33, "D": 34}
 
 
 def _tokens(vocab, n, seed):
@@ -494,7 +501,7 @@ def test_one_mechanism_alone_whole_and_token_by_token(pe, models, name, dtype):
 
 # ---- whole models -----------------------------------------------------------------------------------------------------
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D"])
 def test_whole_prompt_and_its_first_tokens(pe, models, key, dtype):
     eng = models.engine(key, dtype)
     toks = _tokens(CONFIGS[key]["vocab"], 300, 1)
@@ -512,7 +519,7 @@ def test_whole_prompt_and_its_first_tokens(pe, models, key, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D"])
 def test_long_token_by_token_decoding_equals_the_prompt(pe, models, key, dtype):
     """A short prompt, then 240 tokens one by one (past every window, over three page borders, through CUDA graphs),
     against the plain implementation of the whole sequence."""
@@ -542,7 +549,7 @@ def test_a_prompt_fed_in_portions(pe, models, key, dtype, portion):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("key", ["A", "B", "C"])
+@pytest.mark.parametrize("key", ["A", "B", "C", "D"])
 def test_unequal_batches_on_slots_used_again(pe, models, key, dtype):
     """Two batches in a row on the same slots and pages: unequal prompts in one step (among them one token), then one
     token each until the shorter ones have ended; each request against itself alone in the plain implementation."""
