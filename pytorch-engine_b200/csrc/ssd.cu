@@ -25,7 +25,7 @@ struct SsdArgs {
   const int* seq_slot; const int* seq_qstart;
   int n_seqs, heads, groups, n, dv, n_slots;
   int chunk, max_chunks;               // tokens per chunk (0: the whole step in one go)
-  float* scratch;                      // [n_seqs, max_chunks, heads, n * dv] then [n_seqs, max_chunks, heads] log decays
+  float* scratch;                      // [n_seqs, heads, max_chunks, n * dv] then [n_seqs, heads, max_chunks] log decays
   int* status;
 };
 
@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(NR == 0 ? 1024 : 512) ssd_kernel(SsdArgs a) {
     if (MODE == 1 && t1 == q1) return;             // nothing follows the sequence's last chunk
   }
   const size_t unit = (size_t)n * dv;
-  const size_t cidx = ((size_t)b * a.max_chunks + c) * a.heads + head;
+  const size_t cidx = ((size_t)b * a.heads + head) * a.max_chunks + c;      // a head's chunks lie side by side
   float* cs = MODE != 0 ? a.scratch + cidx * unit : nullptr;
   float* gS = a.S + ((size_t)slot * a.heads + head) * unit;
   const float* src = MODE == 0 ? gS : cs;
@@ -221,28 +221,28 @@ __global__ void ssd_chain_kernel(SsdArgs a) {
   const int q_len = a.seq_qstart[b + 1] - a.seq_qstart[b];
   const int n_chunks = (q_len + a.chunk - 1) / a.chunk;
   const size_t unit = (size_t)a.n * a.dv;
-  const size_t per = (size_t)a.heads * unit;          // floats from one chunk's state to the next one's
-  const float* logs = a.scratch + (size_t)a.n_seqs * a.max_chunks * a.heads * unit + (size_t)b * a.max_chunks * a.heads + head;
+  const size_t first = ((size_t)b * a.heads + head) * a.max_chunks;          // the head's first chunk
+  const float* logs = a.scratch + (size_t)a.n_seqs * a.max_chunks * a.heads * unit + first;
   const float* gS = a.S + ((size_t)slot * a.heads + head) * unit;
   // a thread follows one element through the chunks, eight chunks' loads in flight at a time (a chunk's slot is read
   // before it is overwritten with that chunk's true start)
   constexpr int G = 8;
   const size_t e = (size_t)blockIdx.z * blockDim.x + threadIdx.x;
   if (e >= unit) return;
-  float* u = a.scratch + ((size_t)b * a.max_chunks * a.heads + head) * unit + e;
+  float* u = a.scratch + first * unit + e;
   float val = gS[e];
   for (int c0 = 0; c0 < n_chunks; c0 += G) {
     float loc[G], lg[G];
 #pragma unroll
     for (int i = 0; i < G; ++i) {
       const bool has = c0 + i + 1 < n_chunks;
-      loc[i] = has ? u[(size_t)(c0 + i) * per] : 0.f;
-      lg[i] = has ? logs[(size_t)(c0 + i) * a.heads] : 0.f;
+      loc[i] = has ? u[(size_t)(c0 + i) * unit] : 0.f;
+      lg[i] = has ? logs[c0 + i] : 0.f;
     }
 #pragma unroll
     for (int i = 0; i < G; ++i) {
       if (c0 + i >= n_chunks) break;
-      u[(size_t)(c0 + i) * per] = val;
+      u[(size_t)(c0 + i) * unit] = val;
       if (c0 + i + 1 < n_chunks) val = fmaf(expf(lg[i]), val, loc[i]);
     }
   }
