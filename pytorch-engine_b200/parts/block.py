@@ -24,6 +24,31 @@ class DeltaSum:
         ops.rmsnorm_residual_sum(stream, self.deltas, self.scales, weight_like, None, 0.0)
 
 
+class NormedDelta:
+    """A sublayer output that is still to go through a norm of its own and be added to the stream: what a block with a norm
+    behind each sublayer hands on, so that the next block's first norm can do all of it in one kernel.  Whoever gets one and
+    cannot fuse it calls ``settle(stream)``."""
+
+    def __init__(self, delta: torch.Tensor, norm) -> None:
+        self.delta = delta
+        self.norm = norm
+
+    def settle(self, stream: torch.Tensor) -> None:
+        self.norm.add_after(stream, self.delta, None)
+
+
+def settle_pending(stream: torch.Tensor, pending) -> None:
+    """Add what the block before left to be added (nothing, one delta, several scaled ones, one behind a norm)."""
+    if pending is None:
+        return
+    if isinstance(pending, NormedDelta):
+        pending.settle(stream)
+    elif isinstance(pending, DeltaSum):
+        pending.add_into(stream, stream)
+    else:
+        stream.add_(pending)
+
+
 @register("arrangement", "pre_norm")
 class PreNormBlock:
     """``h = x + mixer(norm1(x))``; ``out = h + ffn(norm2(h))`` (pygguf_engine/model.py:1025-1042)."""
@@ -42,6 +67,9 @@ class PreNormBlock:
         """``stream``: float32 residual ``[N, hidden]``, updated in place; ``pending``: the previous
         block's delta that is not added yet (or None).  Returns this block's own pending delta."""
         rt = self.runtime
+        if isinstance(pending, NormedDelta):
+            pending.settle(stream)
+            pending = None
         normed = ctx.buffer("block.normed", tuple(stream.shape), rt.dtype)
         self.mixer_norm.add_forward(stream, pending, normed)
         if writes_cache:
@@ -73,10 +101,7 @@ class PostNormBlock:
     def forward(self, stream: torch.Tensor, pending: Optional[torch.Tensor], ctx, view, writes_cache: bool = True):
         rt = self.runtime
         if pending is not None:       # a block before this one left its last delta to be added
-            if isinstance(pending, DeltaSum):
-                pending.add_into(stream, stream)
-            else:
-                stream.add_(pending)
+            settle_pending(stream, pending)
             ctx.stream_copy = None
         same = rt.dtype == torch.float32
         x = stream
@@ -123,6 +148,9 @@ class ParallelBlock:
 
     def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
         rt = self.runtime
+        if isinstance(pending, NormedDelta):
+            pending.settle(stream)
+            pending = None
         normed = ctx.buffer("block.normed", tuple(stream.shape), rt.dtype)
         self.norm.add_forward(stream, pending, normed)
         deltas = []
@@ -171,11 +199,7 @@ class SandwichDepthBlock:
 
     def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
         rt = self.runtime
-        if pending is not None:       # a block of another arrangement before this one left its last delta to be added
-            if isinstance(pending, DeltaSum):
-                pending.add_into(stream, stream)
-            else:
-                stream.add_(pending)
+        settle_pending(stream, pending)  # a block of another arrangement before this one left its last delta to be added
         n, hidden = stream.shape
         results = ctx.buffer("depth.results", (self.depth + 1, n, hidden), torch.float32)
         work = results[self.index + 1]
@@ -209,8 +233,9 @@ class SandwichBlock:
     Parts by name: ``mixer_norm, post_mixer_norm``, one mixer (``mixer``) or two that read the same input (any two names of
     role "mixer", with ``combine``, a part that makes one output of the two), optionally ``ffn_norm, ffn, post_ffn_norm``, and
     optionally ``inject``: a part of role "stream" that rewrites the stream in front of the block (``inject.forward(stream,
-    ctx)``).  The block adds into the float32 stream itself and hands nothing on.  Where the post norm offers it
-    (``add_after(..., then=)``), the add behind the mixer and the norm in front of the feed-forward are one pass."""
+    ctx)``).  Where the post norm offers it (``add_after(..., then=)``), the add behind a sublayer and the norm in front of
+    the next one are one pass; that holds across blocks too: the block hands its last sublayer's output on as a
+    ``NormedDelta``, and the next block's first norm (or the model's final norm) takes it from there."""
 
     graph_safe = True  # launches only; nothing in forward() waits for the device
 
@@ -231,15 +256,15 @@ class SandwichBlock:
 
     def forward(self, stream: torch.Tensor, pending, ctx, view, writes_cache: bool = True):
         rt = self.runtime
-        if pending is not None:       # a block of another arrangement before this one left its last delta to be added
-            if isinstance(pending, DeltaSum):
-                pending.add_into(stream, stream)
-            else:
-                stream.add_(pending)
-        if self.inject is not None:
-            self.inject.forward(stream, ctx)
         normed = ctx.buffer("block.normed", tuple(stream.shape), rt.dtype)
-        self.mixer_norm.add_forward(stream, None, normed)
+        if isinstance(pending, NormedDelta) and self.inject is None and self.fuses(pending.norm, self.mixer_norm):
+            # the last add of the block before and this block's first norm in one pass
+            pending.norm.add_after(stream, pending.delta, normed, then=self.mixer_norm)
+        else:
+            settle_pending(stream, pending)
+            if self.inject is not None:
+                self.inject.forward(stream, ctx)
+            self.mixer_norm.add_forward(stream, None, normed)
         outs = []
         for i, (name, mixer) in enumerate(zip(self.mixer_names, self.mixers)):
             v = view[name] if isinstance(view, dict) else view
@@ -257,23 +282,21 @@ class SandwichBlock:
                 # the two outputs' mix, the norm on it, the add and the feed-forward's norm in one kernel
                 self.combine.add_after_tanh_norm(outs[0], outs[1], stream, self.post_mixer_norm, self.ffn_norm,
                                                  None if self.ffn is None else normed)
-                if self.ffn is not None:
-                    self.post_ffn_norm.add_after(stream, self.ffn.forward(normed, ctx), None)
                 ctx.stream_copy = None
-                return None
+                return None if self.ffn is None else NormedDelta(self.ffn.forward(normed, ctx), self.post_ffn_norm)
             mixed = self.combine.forward(outs[0], outs[1], ctx.buffer("block.mixed", tuple(outs[0].shape), outs[0].dtype))
+        ctx.stream_copy = None
         if self.ffn is None:
-            self.post_mixer_norm.add_after(stream, mixed, None)
-            ctx.stream_copy = None
-            return None
+            if len(outs) == 2:        # (the mix lies in a buffer of this block's: add it here)
+                self.post_mixer_norm.add_after(stream, mixed, None)
+                return None
+            return NormedDelta(mixed, self.post_mixer_norm)
         if self.fuses(self.post_mixer_norm, self.ffn_norm):
             self.post_mixer_norm.add_after(stream, mixed, normed, then=self.ffn_norm)
         else:
             self.post_mixer_norm.add_after(stream, mixed, None)
             self.ffn_norm.add_forward(stream, None, normed)
-        self.post_ffn_norm.add_after(stream, self.ffn.forward(normed, ctx), None)
-        ctx.stream_copy = None
-        return None
+        return NormedDelta(self.ffn.forward(normed, ctx), self.post_ffn_norm)
 
     @staticmethod
     def fuses(post_norm, next_norm) -> bool:

@@ -32,6 +32,9 @@ class RMSNorm:
 
     def add_forward(self, residual: torch.Tensor, delta: Optional[torch.Tensor], out: torch.Tensor,
                     rows: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if hasattr(delta, "settle"):      # an output that goes through a norm of its own before it is added
+            delta.settle(residual)
+            delta = None
         if hasattr(delta, "deltas"):      # several scaled outputs of a block whose sublayers run side by side
             ops.rmsnorm_residual_sum(residual, delta.deltas, delta.scales, self.weight, out, self.eps, rows)
             return out
@@ -70,7 +73,12 @@ class DynamicTanh:
 
     def add_forward(self, residual: torch.Tensor, delta, out: torch.Tensor, rows: Optional[torch.Tensor] = None) -> torch.Tensor:
         if delta is not None:
-            if hasattr(delta, "deltas"):
+            if hasattr(delta, "settle"):
+                if rows is None and type(delta.norm) is type(self):
+                    delta.norm.add_after(residual, delta.delta, out, then=self)     # its norm, the add and this norm in one pass
+                    return out
+                delta.settle(residual)
+            elif hasattr(delta, "deltas"):
                 delta.add_into(residual, self.weight)
             else:
                 residual.add_(delta)

@@ -544,7 +544,7 @@ def test_toy_block_arrangement(pe):
                                         "qk_norm": False, "eps": eps, "scale": None, "window": None, "position": "rope"},
                           {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj")})
         ffn = lambda i: P("swiglu", {"hidden": h, "intermediate": 2 * h}, {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"})
-        blocks = (B.standard("parallel", norm("l0.n1"), att(0), norm("l0.n2"), ffn(0), name="parallel"),
+        blocks = (B.standard("test_parallel", norm("l0.n1"), att(0), norm("l0.n2"), ffn(0), name="parallel"),
                   B.standard("pre_norm", norm("l1.n1"), att(1), norm("l1.n2"), ffn(1), name="sequential"))
         return pe.parts.ModelPlan(
             hidden_size=h, vocab_size=c.vocab_size, max_positions=c.max_position_embeddings,
@@ -553,7 +553,7 @@ def test_toy_block_arrangement(pe):
             head=P("linear_head", {"vocab": c.vocab_size, "hidden": h}, {"weight": "emb"}),
             positions={"rope": P("rope", {"rotary_dim": d, "theta": theta, "max_positions": c.max_position_embeddings})})
 
-    pe.parts.register("arrangement", "parallel", ParallelBlock, replace=True)
+    pe.parts.register("arrangement", "test_parallel", ParallelBlock, replace=True)   # (a name of the test's own: the package has a "parallel")
     pe.register_architecture("ToyParallelLM", ToyMixConfig, plan, replace=True)
     try:
         eng = pe.Engine.from_random(cfg, seed=12, dtype="float32", max_cache_tokens=256, max_batch=2)
@@ -584,7 +584,7 @@ def test_toy_block_arrangement(pe):
         eng.free_slot(s)
         assert rel_err(torch.cat(lg), plain_toy(toks)[[0, 6, 7, 8, 9, 10]]) < 1e-5
     finally:
-        pe.parts.unregister("arrangement", "parallel")
+        pe.parts.unregister("arrangement", "test_parallel")
         pe.config.unregister_architecture("ToyParallelLM")
 
 
@@ -737,7 +737,7 @@ def test_toy_learned_positions_and_a_block_with_four_norms(pe):
             {k: f"l{i}.{k}" for k in ("q_proj", "k_proj", "v_proj", "o_proj", "q_norm", "k_norm")})
         ffn = lambda i: P("swiglu", {"hidden": h, "intermediate": 2 * h},
                           {"gate_proj": f"l{i}.g", "up_proj": f"l{i}.u", "down_proj": f"l{i}.d"})
-        sandwich = B("sandwich", {"pre_mixer": ("norm", norm("l0.n1")), "mixer": ("mixer", att(0, "learned")),
+        sandwich = B("test_sandwich", {"pre_mixer": ("norm", norm("l0.n1")), "mixer": ("mixer", att(0, "learned")),
                                   "post_mixer": ("norm", norm("l0.n1b")), "pre_ffn": ("norm", norm("l0.n2")),
                                   "ffn": ("feed_forward", ffn(0)), "post_ffn": ("norm", norm("l0.n2b"))}, name="sandwich")
         usual = B.standard("pre_norm", norm("l1.n1"), att(1, "rope"), norm("l1.n2"), ffn(1), name="usual")
@@ -751,7 +751,7 @@ def test_toy_learned_positions_and_a_block_with_four_norms(pe):
                                     {"table": "pos.table"})})
 
     pe.parts.register("position", "learned_abs", LearnedAbsolutePosition, replace=True)
-    pe.parts.register("arrangement", "sandwich", SandwichBlock, replace=True)
+    pe.parts.register("arrangement", "test_sandwich", SandwichBlock, replace=True)   # (the package has a "sandwich")
     pe.register_architecture("ToySandwichLM", ToyMixConfig, plan, replace=True)
     try:
         eng = pe.Engine.from_random(cfg, seed=21, dtype="float32", max_cache_tokens=256, max_batch=2)
@@ -804,7 +804,7 @@ def test_toy_learned_positions_and_a_block_with_four_norms(pe):
             assert rel_err(torch.stack(got[1]), refs[1][[1, 2, 3, 4, 5]]) < 1e-5
     finally:
         pe.parts.unregister("position", "learned_abs")
-        pe.parts.unregister("arrangement", "sandwich")
+        pe.parts.unregister("arrangement", "test_sandwich")
         pe.config.unregister_architecture("ToySandwichLM")
 
 
