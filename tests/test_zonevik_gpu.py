@@ -66,7 +66,7 @@ CONFIGS = {
     "B": {"architecture": "Zonevik", "vocab": 256, "width": 128, "norm": {"eps": 1e-6},
           "layers": [
               {"type": "delta", "mixer": {"heads": 4, "kv_heads": 4, "dim": 64, "vdim": 64, "conv": 1}, "mlp": _moe(8, 2, 64, (2, 1))},
-              {"type": "attention", "mixer": _att(4, 2, 64, 64, 0.125, 64, 50000.0, (2.0, 128, 8.0, 1.0)), "mlp": _moe(8, 3, 64, (8, 5))},
+              {"type": "attention", "mixer": _att(4, 2, 64, 64, 0.125, 64, 30000.0, (2.0, 128, 8.0, 1.0)), "mlp": _moe(8, 3, 64, (8, 5))},
               {"type": "parallel", "mixer": {"left": _left(4, 2, 64, 64, 0.125, 100, 70), "right": _right(4, 64, 128, 1, 4, 1)},
                "mlp": _moe(4, 2, 128)}]},
     "C": {"architecture": "Zonevik", "vocab": 90, "width": 48, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.5},
